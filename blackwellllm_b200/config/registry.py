@@ -1,8 +1,8 @@
 """One registry from an architecture's name to how its config.json becomes a model.
 
 ``register_architecture(name, parse)`` stores ``parse(raw_json) -> ModelConfig``.
-``load_config`` reads ``config.json`` and dispatches on ``architectures[0]``,
-falling back to ``model_type`` (the reference keys on ``model_type`` strings
+``load_config`` reads ``config.json`` and dispatches on ``architectures[0]`` (or the string
+``architecture``), falling back to ``model_type`` (the reference keys on ``model_type`` strings
 only: src/core/config.cpp:81,226-227); end-of-sequence ids that a
 ``generation_config.json`` in the same folder lists are added to config.json's.
 """
@@ -37,6 +37,8 @@ def registered_architectures() -> tuple:
 
 def parse_config(raw: Mapping[str, Any]) -> ModelConfig:
     archs = raw.get("architectures") or []
+    if not archs and isinstance(raw.get("architecture"), str):   # some configurations name one, as a string
+        archs = [raw["architecture"]]
     name = None
     if archs:
         if archs[0] in _ARCHITECTURES:

@@ -31,11 +31,29 @@ class Llama3RopeScaling:
 
 
 @dataclass(frozen=True)
+class YarnRopeScaling:
+    """Rescaling of rotary frequencies by how often a pair turns within the original context.
+
+    With ``pair(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta)``, ``lo = max(floor(pair(fast)), 0)``
+    and ``hi = min(ceil(pair(slow)), rotary_dim - 1)``, pair i gets ``ramp_i = clamp((i - lo) / max(hi - lo,
+    0.001), 0, 1)`` and the frequency ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``; cosines and sines are
+    multiplied by ``0.1 ln(factor) + 1``.
+    """
+    factor: float
+    original: int
+    fast: float
+    slow: float
+    kind: str = "yarn"
+
+
+@dataclass(frozen=True)
 class RopeSpec:
-    """rotate_half rotary position encoding over the first ``rotary_dim`` channels."""
+    """Rotary position encoding over the first ``rotary_dim`` channels of a head.  Channel i turns with
+    channel i + rotary_dim / 2 (rotate_half), or with ``interleaved`` channel 2i with 2i + 1."""
     theta: float
     rotary_dim: int
-    scaling: Optional[Llama3RopeScaling] = None
+    scaling: Optional[Any] = None   # Llama3RopeScaling | YarnRopeScaling
+    interleaved: bool = False
     kind: str = "rope"
 
 
@@ -49,6 +67,7 @@ class NoPositionSpec:
 class RMSNormSpec:
     eps: float
     kind: str = "rmsnorm"
+    param: str = "weight"   # the gain's name below the norm's prefix
 
 
 @dataclass(frozen=True)
@@ -66,6 +85,50 @@ class AttentionSpec:
     window: Optional[int] = None
     softmax_scale: Optional[float] = None  # None -> head_dim ** -0.5
     kind: str = "gqa_attention"
+    # ``chunk``: a query sees no key before the start of its own block of ``chunk`` positions (blocks are
+    # counted from position 0 of the sequence).  ``v_head_dim``: the value size of a head where it differs
+    # from the query/key size ``head_dim``.  ``qk_norm_eps``: RMS norm with a gain per channel over the
+    # WHOLE query projection of a token (all heads at once), and over the whole key projection, before the
+    # rotation.  ``names``: the tensors' names below the mixer's prefix, as (role, name) pairs for
+    # q, k, v, o, q_bias, k_bias, v_bias, q_norm, k_norm (default: q_proj.weight, q_proj.bias, ...).
+    chunk: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    qk_norm_eps: Optional[float] = None
+    names: Tuple[Tuple[str, str], ...] = ()
+
+
+@dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """A recurrent mixer with a [key_dim, value_dim] state per head and a decay per key channel:
+    ``S <- diag(a) S + k v^T``, ``o = S^T q / sqrt(key_dim)``, ``a = sigmoid(W2 (W1 x) + b) ** (1 / tau)``;
+    each head's output is RMS-normed over value_dim (one gain shared by the heads), multiplied by
+    ``silu(W_g x)`` and projected.  ``decay_rank``: the inner size of the decay's two projections
+    (None: whatever the stored tensors have)."""
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    tau: float
+    norm_eps: float
+    decay_rank: Optional[int] = None
+    kind: str = "gated_linear_attention"
+    names: Tuple[Tuple[str, str], ...] = ()
+
+
+@dataclass(frozen=True)
+class RoutedFFNSpec:
+    """Mixture of experts: ``num_experts`` gated feed-forwards ``down(silu(gate u) * (up u))`` without biases,
+    of which each token uses the ``top_k`` with the largest router scores.  ``score``: "sigmoid" or
+    "softmax" of the float32 router logits; ``renormalize``: the chosen scores are divided by their sum;
+    ``scale_input``: the score multiplies what the expert reads (u = s x) instead of what it returns."""
+    num_experts: int
+    top_k: int
+    expert_size: int
+    score: str = "sigmoid"
+    renormalize: bool = False
+    scale_input: bool = False
+    kind: str = "routed_ffn"
+    router_name: str = "router"
+    expert_names: Tuple[str, str, str, str] = ("e{e}.", "gate", "up", "down")
 
 
 @dataclass(frozen=True)
@@ -80,7 +143,7 @@ class LayerSpec:
     """One layer: which mixer, which feed-forward, which norms, arranged how.
 
     ``block`` names the arrangement (``"prenorm"``: x += mixer(norm(x));
-    x += ffn(norm(x))).  ``ffn`` may be ``None`` for a mixer-only layer.
+    x += ffn(norm(x)); ``"sandwich"``: the same with a second norm on each sublayer's output).  ``ffn`` may be ``None`` for a mixer-only layer.
     """
     mixer: Any
     ffn: Any
@@ -92,6 +155,12 @@ class LayerSpec:
     ffn_prefix: str = "mlp."
     mixer_norm_prefix: str = "input_layernorm."
     ffn_norm_prefix: str = "post_attention_layernorm."
+    # the "sandwich" arrangement norms each sublayer's OUTPUT too before it is added to the stream:
+    # x += post(mixer(pre(x))); x += post(ffn(pre(x)))
+    mixer_post_norm: Any = None
+    ffn_post_norm: Any = None
+    mixer_post_norm_prefix: str = ""
+    ffn_post_norm_prefix: str = ""
 
 
 @dataclass(frozen=True)
@@ -102,6 +171,9 @@ class ScheduleEntry:
     """
     layer: int
     cache_of: Optional[int] = None
+    # the embedding's output (the stream as it was before the first run) is added to the stream right
+    # before this run: the start of a repeated pass over a stretch of layers
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -41,7 +41,7 @@ struct Params {
     const int* cu_q; const int* q_start; const int* kv_len; const int* block_table;
     const int* work;              // int4 per item
     float* part_o; float* part_ml; // slices' partial results (attn_keys_kernel)
-    int max_blocks, nh, nkv, G, page_size, num_pages, window;
+    int max_blocks, nh, nkv, G, page_size, num_pages, window, chunk;
     float scale_log2;
     // Decode rows straight from the q/k/v product (attn_keys_tma_kernel only; null: q holds the queries and
     // the cache this step's keys and values): qkv is float32 [planes][tokens][(nh + 2 nkv) * HD] to be added
@@ -241,7 +241,7 @@ __device__ __forceinline__ void init_rows(const Params& p, RowState& st, int row
         st.m[h] = -INFINITY; st.l[h] = 0.f;
         if (row < n_rows) {
             st.qpos[h] = q_pos0 + row / p.G;
-            st.lo[h] = p.window > 0 ? max(0, st.qpos[h] - p.window + 1) : 0;
+            st.lo[h] = bw::first_visible(st.qpos[h], p.window, p.chunk);
         } else { st.qpos[h] = -1; st.lo[h] = 0; }
     }
 }
@@ -269,7 +269,7 @@ attn_rows_kernel(Params p, int toks_per_tile) {
     cp_async_commit();
 
     const int last_pos = q_pos0 + ntok - 1;
-    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
     const int t_lo = first_key / BN, t_hi = last_pos / BN;   // inclusive
     load_kv_tile(p, bt, g, kv_len, t_lo * BN, kv, kv + TILE_BYTES);
     cp_async_commit();
@@ -298,7 +298,7 @@ attn_rows_kernel(Params p, int toks_per_tile) {
         if (warp_live && t * BN <= warp_last_pos) {
             const int warp_first_pos = q_pos0 + (warp * 16) / p.G;
             const bool need_mask = (t * BN + BN - 1 > warp_first_pos) ||
-                                   (p.window > 0 && t * BN < warp_last_pos - p.window + 1);
+                                   (t * BN < bw::first_visible(warp_last_pos, p.window, p.chunk));
             process_keys<BN>(qf, k_tile, k_tile + TILE_BYTES, 0, t * BN, need_mask, p.scale_log2, st, o);
         }
         __syncthreads();
@@ -390,7 +390,7 @@ attn_keys_kernel(Params p) {
     const int* bt = p.block_table + (size_t)r * p.max_blocks;
 
     const int last_pos = q_pos0 + q_len - 1;
-    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
     const int t_first = first_key / BN, t_end = last_pos / BN + 1;
     const int per = (t_end - t_first + n_slices - 1) / n_slices;
     const int t_lo = t_first + slice * per, t_hi = min(t_end, t_lo + per) - 1;   // inclusive; may be empty
@@ -420,7 +420,7 @@ attn_keys_kernel(Params p) {
             __syncthreads();
             const int k_off = warp * 16;
             if (t * BN + k_off <= last_pos) {
-                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (p.window > 0 && t * BN < last_pos - p.window + 1);
+                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (t * BN < bw::first_visible(last_pos, p.window, p.chunk));
                 process_keys<16>(qf, k_tile, k_tile + TILE_BYTES, k_off, t * BN, need_mask, p.scale_log2, st, o);
             }
             __syncthreads();
@@ -642,7 +642,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
     const int q_pos0 = p.q_start[r];
     const int* bt = p.block_table + (size_t)r * p.max_blocks;
     const int last_pos = q_pos0 + q_len - 1;
-    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
     const int t_first = first_key / BN, t_end = last_pos / BN + 1;
     const int per = (t_end - t_first + n_slices - 1) / n_slices;
     const int t_lo = t_first + slice * per, t_hi = min(t_end, t_lo + per) - 1;   // inclusive; may be empty
@@ -723,7 +723,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             // Rows of keys that do not exist hold whatever was there: values times a probability of
             // 0 must still be 0, so those rows of V are cleared (only in a request's last tile or at
             // a window's edge).
-            if (t * BN + BN > kv_len || (p.window > 0 && t * BN < first_key)) {
+            if (t * BN + BN > kv_len || (t * BN < first_key)) {
                 for (int idx = threadIdx.x; idx < BN * NSL * 8; idx += THREADS) {
                     const int rk = idx / (NSL * 8), rem = idx - rk * (NSL * 8);
                     const int key = t * BN + rk;
@@ -734,7 +734,7 @@ attn_keys_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
             }
             const int k_off = warp * 16;
             if (ok && t * BN + k_off <= last_pos) {
-                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (p.window > 0 && t * BN < last_pos - p.window + 1);
+                const bool need_mask = (t * BN + BN - 1 > q_pos0) || (t * BN < bw::first_visible(last_pos, p.window, p.chunk));
                 process_keys_swz<16>(qf, k_tile, v_tile, k_off, t * BN, need_mask, p.scale_log2, st, o);
             }
             // every warp is done with this stage before it is loaded again; a timeout ends the loop for all
@@ -875,7 +875,7 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 // keys_work: n_keys_items int4 (request, slice, slices, item) for the others; merge_work: one int4 per
 // item that has more than one slice (merge_max_slices: the most slices any of them has, 0: unknown).
 // part_o / part_ml: float32 scratch for
-// [items, nkv, slices, 16, HD] and [.., 2].  window <= 0: all keys.
+// [items, nkv, slices, 16, HD] and [.., 2].  window <= 0: no window; chunk <= 0: no blocks (bw::first_visible).
 // qkv != null (q may be null then): every request has ONE token, and its queries, key and value come from
 // the q/k/v product itself: float32 [qkv_planes][tokens][(nh + 2 nkv) * HD], the planes qkv_plane_stride
 // floats apart and added in order, the rotated channels of the q and k heads as (j, j + rd / 2) pairs;
@@ -886,7 +886,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
                                const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                                const int* rows_work, int n_rows_items, const int* keys_work, int n_keys_items,
                                const int* merge_work, int n_merge_items, float* part_o, float* part_ml, int nh,
-                               int nkv, int page_size, int num_pages, int window, float scale,
+                               int nkv, int page_size, int num_pages, int window, int chunk, float scale,
                                const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
                                int rd, int append, int merge_max_slices, void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
@@ -909,7 +909,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.cu_q = cu_q; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
     p.part_o = part_o; p.part_ml = part_ml;
     p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size; p.num_pages = num_pages;
-    p.window = window > 0 ? window : 0;
+    p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.qkv = qkv; p.qkv_plane_stride = qkv_plane_stride; p.rope_table = rope_table;
     p.qkv_planes = qkv_planes; p.rd = rd; p.append = append;

@@ -54,7 +54,7 @@ __device__ int g_status = 0;
 struct Params {
     bf16* out;
     const int* cu_q; const int* q_start; const int* kv_len; const int* block_table; const int* work;
-    int max_blocks, nh, nkv, G, page_size, window, tpt;
+    int max_blocks, nh, nkv, G, page_size, window, chunk, tpt;
     float scale_log2;
 };
 
@@ -121,7 +121,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     const int n_rows = ntok * p.G;
     const int q_pos0 = p.q_start[r] + tok0;
     const int last_pos = q_pos0 + ntok - 1;
-    const int first_key = p.window > 0 ? max(0, q_pos0 - p.window + 1) : 0;
+    const int first_key = bw::first_visible(q_pos0, p.window, p.chunk);
     const int t_lo = first_key / BN, n_tiles = last_pos / BN - t_lo + 1;
     const int* bt = p.block_table + (size_t)r * p.max_blocks;
 
@@ -221,7 +221,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         const bool row_ok = row < n_rows;
         const int tok = row / p.G, hg = row - tok * p.G;
         const int qpos = q_pos0 + tok;
-        const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+        const int lo = bw::first_visible(qpos, p.window, p.chunk);
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
         float m = -INFINITY, l = 0.f;   // m: the reference of the exponents (at most 8 below the row maximum)
         bool ok = true;
@@ -230,7 +230,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             if (!__all_sync(0xffffffffu, bw::mbar_wait(s_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 16))) { ok = false; break; }
             bw::tc_fence_after();
             const int key0 = (t_lo + i) * BN;
-            const bool need_mask = !row_ok || (key0 + BN - 1 > q_pos0) || (p.window > 0 && key0 < last_pos - p.window + 1);
+            const bool need_mask = !row_ok || (key0 + BN - 1 > q_pos0) || (key0 < bw::first_visible(last_pos, p.window, p.chunk));
             // The row of S, unscaled (scale > 0, so the maximum commutes with it; masked keys become -inf).
             // It stays in these 64 registers; the packed probabilities take the place of the first 32
             // as they are made, so that the kernel stays within 128 registers (see the launch bounds).
@@ -290,7 +290,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             // Values of keys that do not exist (past the request's length, or on a page the block
             // table no longer holds) are whatever the stand-in page contained: zero them, since a
             // probability of 0 times a stale NaN would still be NaN.  Rare: the last tile, a window's edge.
-            if (key0 + BN > kv_len || (p.window > 0 && key0 < first_key)) {
+            if (key0 + BN > kv_len || (key0 < first_key)) {
                 if (!__all_sync(0xffffffffu, bw::mbar_wait(v_full + 8 * (i & 1), (i >> 1) & 1, &g_status, 21))) { ok = false; break; }
                 for (int pg = 0; pg < BN / p.page_size; ++pg) {
                     const int pkey = key0 + pg * p.page_size;
@@ -383,7 +383,7 @@ BW_EXPORT int bw_attention_tc_supported(int nh, int nkv, int page_size) {
 BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                               const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                               const int* work, int n_items, int T, int nh, int nkv, int page_size, int num_pages,
-                              int window, float scale, void* stream) {
+                              int window, int chunk, float scale, void* stream) {
     if (n_items <= 0) return 0;
     if (!bw_attention_tc_supported(nh, nkv, page_size) || !(scale > 0.f)) return BW_ERR_UNSUPPORTED;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return BW_ERR_UNSUPPORTED;
@@ -406,7 +406,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     Params p;
     p.out = (bf16*)out; p.cu_q = cu_q; p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
     p.work = work; p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size;
-    p.window = window > 0 ? window : 0; p.tpt = tpt;
+    p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0; p.tpt = tpt;
     p.scale_log2 = scale * 1.4426950408889634f;
     bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();

@@ -103,6 +103,14 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     return launch_opt(true, kernel, grid, block, smem, stream, std::forward<Args>(args)...);
 }
 
+// The first key position a query at q_pos may see: a sliding window of `window` keys (0: none) and / or
+// blocks of `chunk` positions, counted from position 0, that a query does not look out of (0: none).
+__host__ __device__ __forceinline__ int first_visible(int q_pos, int window, int chunk) {
+    int lo = (window > 0 && q_pos - window + 1 > 0) ? q_pos - window + 1 : 0;
+    if (chunk > 0) { const int c0 = q_pos - q_pos % chunk; if (c0 > lo) lo = c0; }
+    return lo;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);   // lo in the low half
     return *reinterpret_cast<const uint32_t*>(&v);

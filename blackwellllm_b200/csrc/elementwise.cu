@@ -192,7 +192,7 @@ __global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, i
 // cos and sin of pos * inv_freq[j] for every token of the step: [T, rotary_dim] (cos, then sin).
 // All layers with the same rotary parameters share one table per step.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float* __restrict__ table, int rotary_dim, int T) {
+                                  float* __restrict__ table, int rotary_dim, int T, float magnitude) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     const int half = rotary_dim >> 1;
@@ -201,8 +201,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     const int t = idx / half, j = idx - t * half;
     float s, c;
     sincosf((float)positions[t] * inv_freq[j], &s, &c);
-    table[(size_t)t * rotary_dim + j] = c;
-    table[(size_t)t * rotary_dim + half + j] = s;
+    table[(size_t)t * rotary_dim + j] = c * magnitude;
+    table[(size_t)t * rotary_dim + half + j] = s * magnitude;
 }
 
 // Where each token of the step keeps its keys and values: page * page_size + slot of its position,
@@ -303,6 +303,23 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
     }
 }
 
+// ---------------------------------------------------------------- norm of a branch, added to the stream
+// stream[i] += x[i] * rsqrt(mean(x[i]^2) + eps) * w  (the norm that FOLLOWS a sublayer).  One block per row.
+template <typename WT>
+__global__ void rmsnorm_add_kernel(const float* __restrict__ x, const WT* __restrict__ w, float* __restrict__ stream,
+                                   int H, float eps) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    __shared__ float scratch[32];
+    const float* xr = x + (size_t)blockIdx.x * H;
+    float* o = stream + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) { float v = xr[c]; ss = fmaf(v, v, ss); }
+    ss = bw::block_sum(ss, scratch);
+    const float r = rsqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] += xr[c] * r * bw::to_f32(w[c]);
+}
+
 // ---------------------------------------------------------------- logits
 // In place: x * scale, then cap * tanh(x / cap) when cap > 0 (a model's logit multiplier and soft cap).
 __global__ void logit_transform_kernel(float* __restrict__ x, long long n, float scale, float cap) {
@@ -389,6 +406,19 @@ BW_EXPORT int bw_add_rmsnorm(float* x, const float* planes, int n_planes, long l
 }
 
 // x[total] += the planes, added in plane order
+BW_EXPORT int bw_rmsnorm_add(const float* x, const void* w, int w_type, float* stream_rows, int n, int H, float eps,
+                             void* stream) {
+    if (n <= 0) return 0;
+    if (H <= 0) return BW_ERR_BAD_ARG;
+    const int threads = H >= 1024 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_type == BW_F32) bw::launch((rmsnorm_add_kernel<float>), dim3(n), dim3(threads), 0, s, x, (const float*)w, stream_rows, H, eps);
+    else if (w_type == BW_BF16) bw::launch((rmsnorm_add_kernel<bf16>), dim3(n), dim3(threads), 0, s, x, (const bf16*)w, stream_rows, H, eps);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
 BW_EXPORT int bw_add_planes(float* x, const float* planes, int n_planes, long long plane_stride, long long total,
                             void* stream) {
     if (total <= 0 || n_planes <= 0) return 0;
@@ -414,12 +444,14 @@ BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, in
     return 0;
 }
 
+// magnitude: a factor on every cosine and sine (1 for plain rotary encoding; frequency rescalings that
+// lengthen the context may ask for another)
 BW_EXPORT int bw_rope_table(const int* positions, const float* inv_freq, float* table, int rotary_dim, int T,
-                            void* stream) {
+                            float magnitude, void* stream) {
     if (T <= 0 || rotary_dim <= 0) return 0;
     if (rotary_dim & 1) return BW_ERR_BAD_ARG;
     const int total = T * (rotary_dim / 2);
-    bw::launch((rope_table_kernel), dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, positions, inv_freq, table, rotary_dim, T);
+    bw::launch((rope_table_kernel), dim3((total + 255) / 256), dim3(256), 0, (cudaStream_t)stream, positions, inv_freq, table, rotary_dim, T, magnitude);
     BW_LAUNCH_CHECK();
     return 0;
 }

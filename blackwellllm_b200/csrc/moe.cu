@@ -1,0 +1,267 @@
+// Routed feed-forward (mixture of experts): router scores, the choice of experts, the regrouping of
+// the step's tokens by expert, the experts' two matrix products over the regrouped rows, and the sum of
+// each token's expert outputs.  Nothing here goes through the host: the number of rows an expert gets is
+// known on the device only, so the kernels are launched for the worst case and idle tiles return at once
+// (a decode step stays capturable in a CUDA graph).
+//
+//   moe_route    one warp per token: score = sigmoid(logit) (or softmax), the `top` largest scores
+//                (lowest index on ties), optionally renormalised to sum 1; float32 throughout
+//   moe_plan     one block: rows per expert, each expert's stretch padded to whole tiles of TILE_M rows,
+//                the place of every (token, choice) row, and the expert of every tile
+//   moe_scatter  the regrouped operand: row (token, choice) = weight * x[token] (input scaling) or x[token]
+//   moe_gemm     C[row, :] = A[row, :] W[expert of row]^T, optionally as silu(A Wg^T) * (A Wu^T);
+//                float32 sums on the CUDA cores from float32 or bfloat16 operands
+//   moe_combine  out[token] = sum over choices (in order) of (weight *) C[row of (token, choice)], written,
+//                added to a stream, or normalised (RMS, gain) and then added to a stream
+#include "common.cuh"
+
+using bf16 = __nv_bfloat16;
+
+namespace {
+
+constexpr int TILE_M = 64;   // rows of a tile of regrouped tokens; also the padding of an expert's stretch
+constexpr int BN = 64, BK = 16;
+
+// ---------------------------------------------------------------- routing
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int softmax, int renorm,
+                 int* __restrict__ sel, float* __restrict__ wt) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * E;
+    float zmax = -INFINITY, zsum = 0.f;
+    if (softmax) {
+        for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+        zmax = bw::warp_max(zmax);
+        for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
+        zsum = bw::warp_sum(zsum);
+    }
+    float total = 0.f;
+    int last = -1; float last_s = INFINITY;   // choices are taken in order of (score descending, index ascending)
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float s = softmax ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
+            const bool after = (s < last_s) || (s == last_s && e > last);   // not chosen yet
+            if (after && (s > best || (s == best && e < bi))) { best = s; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        last = bi; last_s = best; total += best;
+        if (lane == 0) { sel[(size_t)t * top + k] = bi; wt[(size_t)t * top + k] = best; }
+    }
+    if (renorm && lane == 0 && total > 0.f)
+        for (int k = 0; k < top; ++k) wt[(size_t)t * top + k] /= total;
+}
+
+// ---------------------------------------------------------------- plan
+// pos_of[n] for the n = T * top rows (token-major); tile_expert[max_tiles] (-1: idle tile).
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ sel, int n, int E, int max_tiles, int* __restrict__ pos_of,
+                int* __restrict__ tile_expert) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    extern __shared__ int sh[];
+    int* count = sh;          // [E]
+    int* start = sh + E;      // [E + 1], in rows
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = sel[i];
+        pos_of[i] = (e >= 0 && e < E) ? atomicAdd(&count[e], 1) : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + TILE_M - 1) / TILE_M * TILE_M; }
+        start[E] = at;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int e = sel[i];
+        if (e >= 0 && e < E) pos_of[i] += start[e];
+    }
+    for (int tile = threadIdx.x; tile < max_tiles; tile += blockDim.x) {
+        const int row = tile * TILE_M;
+        int e = -1;
+        if (row < start[E]) {
+            int lo = 0, hi = E - 1;            // the last expert whose stretch starts at or before row
+            while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (start[mid] <= row) lo = mid; else hi = mid - 1; }
+            e = lo;
+            if (row >= start[e] + count[e]) e = -1;   // wholly inside an expert's padding (cannot happen: padding < TILE_M)
+        }
+        tile_expert[tile] = e;
+    }
+}
+
+// ---------------------------------------------------------------- scatter
+template <typename XT>
+__global__ void __launch_bounds__(256)
+moe_scatter_kernel(const XT* __restrict__ x, const int* __restrict__ pos_of, const float* __restrict__ wt,
+                   XT* __restrict__ xs, int H, int top, int scale_input) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const int i = blockIdx.x;                 // (token, choice)
+    const int t = i / top;
+    const float w = scale_input ? wt[i] : 1.f;
+    const XT* src = x + (size_t)t * H;
+    XT* dst = xs + (size_t)pos_of[i] * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = bw::from_f32<XT>(bw::to_f32(src[c]) * w);
+}
+
+// ---------------------------------------------------------------- grouped product
+// A [rows, K], W [E, N, K] (and W2 the same for GATED), C [rows, N].  grid (max_tiles, ceil(N / BN)).
+template <typename AT, typename CT, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const AT* __restrict__ A, const AT* __restrict__ W, const AT* __restrict__ W2,
+                const int* __restrict__ tile_expert, CT* __restrict__ C, int N, int K) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    __shared__ float As[BK][TILE_M + 4];
+    __shared__ float Bs[BK][BN + 4];
+    __shared__ float B2s[GATED ? BK : 1][BN + 4];
+    const int row0 = blockIdx.x * TILE_M, n0 = blockIdx.y * BN;
+    const AT* Wb = W + (size_t)e * N * K;
+    const AT* W2b = GATED ? W2 + (size_t)e * N * K : nullptr;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;   // 16 x 16 threads, 4 x 4 outputs each
+    float acc[4][4] = {}, acc2[GATED ? 4 : 1][4] = {};
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int idx = threadIdx.x; idx < TILE_M * BK; idx += 256) {
+            const int m = idx / BK, kk = idx % BK;
+            As[kk][m] = (k0 + kk < K) ? bw::to_f32(A[(size_t)(row0 + m) * K + k0 + kk]) : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < BN * BK; idx += 256) {
+            const int nn = idx / BK, kk = idx % BK;
+            const bool ok = n0 + nn < N && k0 + kk < K;
+            Bs[kk][nn] = ok ? bw::to_f32(Wb[(size_t)(n0 + nn) * K + k0 + kk]) : 0.f;
+            if constexpr (GATED) B2s[kk][nn] = ok ? bw::to_f32(W2b[(size_t)(n0 + nn) * K + k0 + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[4], b[4], b2[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Bs[kk][tx * 4 + i]; if constexpr (GATED) b2[i] = B2s[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                    if constexpr (GATED) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if constexpr (GATED) v = v / (1.f + expf(-v)) * acc2[i][j];
+            C[(size_t)(row0 + ty * 4 + i) * N + n] = bw::from_f32<CT>(v);
+        }
+}
+
+// ---------------------------------------------------------------- combine
+// mode 0: out = sum; 1: out += sum; 2: out += sum / rms(sum) * gain.  One block per token.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, const float* __restrict__ wt,
+                   int top, int scale_output, float* __restrict__ out, int H, int mode,
+                   const float* __restrict__ gain, float eps) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    extern __shared__ float row[];    // [H]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const float w = scale_output ? wt[(size_t)t * top + k] : 1.f;
+            v = fmaf(w, y[(size_t)pos_of[(size_t)t * top + k] * H + c], v);
+        }
+        row[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    float r = 1.f;
+    if (mode == 2) r = rsqrtf(bw::block_sum(ss, scratch) / (float)H + eps);
+    float* o = out + (size_t)t * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {   // each thread reads back what it wrote
+        const float v = row[c];
+        if (mode == 0) o[c] = v;
+        else if (mode == 1) o[c] += v;
+        else o[c] += v * r * gain[c];
+    }
+}
+
+}  // namespace
+
+BW_EXPORT int bw_moe_tile_rows() { return TILE_M; }
+
+BW_EXPORT int bw_moe_route(const float* logits, int T, int E, int top, int softmax, int renorm, int* sel, float* wt,
+                           void* stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E) return BW_ERR_BAD_ARG;
+    bw::launch((moe_route_kernel), dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, T, E, top, softmax, renorm, sel, wt);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_moe_plan(const int* sel, int n, int E, int max_tiles, int* pos_of, int* tile_expert, void* stream) {
+    if (n <= 0) return 0;
+    if (E <= 0 || E > 4096 || max_tiles < (n + TILE_M - 1) / TILE_M + E) return BW_ERR_BAD_ARG;
+    bw::launch((moe_plan_kernel), dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), (cudaStream_t)stream, sel, n, E, max_tiles,
+               pos_of, tile_expert);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_moe_scatter(const void* x, int type, const int* pos_of, const float* wt, void* xs, int n, int H, int top,
+                             int scale_input, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (type == BW_F32) bw::launch((moe_scatter_kernel<float>), dim3(n), dim3(256), 0, s, (const float*)x, pos_of, wt, (float*)xs, H, top, scale_input);
+    else if (type == BW_BF16) bw::launch((moe_scatter_kernel<bf16>), dim3(n), dim3(256), 0, s, (const bf16*)x, pos_of, wt, (bf16*)xs, H, top, scale_input);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// type: element type of A and the weights; c_type: of C.  w2 non-null: C = silu(A w^T) * (A w2^T).
+BW_EXPORT int bw_moe_gemm(const void* A, const void* w, const void* w2, int type, const int* tile_expert, void* C, int c_type,
+                          int max_tiles, int N, int K, void* stream) {
+    if (max_tiles <= 0) return 0;
+    if (N <= 0 || K <= 0) return BW_ERR_BAD_ARG;
+    const dim3 grid(max_tiles, (N + BN - 1) / BN);
+    cudaStream_t s = (cudaStream_t)stream;
+#define BW_MG(AT, CT, G) bw::launch((moe_gemm_kernel<AT, CT, G>), grid, dim3(256), 0, s, (const AT*)A, (const AT*)w, (const AT*)w2, tile_expert, (CT*)C, N, K)
+    if (type == BW_F32 && c_type == BW_F32) { if (w2) BW_MG(float, float, true); else BW_MG(float, float, false); }
+    else if (type == BW_BF16 && c_type == BW_BF16) { if (w2) BW_MG(bf16, bf16, true); else BW_MG(bf16, bf16, false); }
+    else if (type == BW_BF16 && c_type == BW_F32) { if (w2) BW_MG(bf16, float, true); else BW_MG(bf16, float, false); }
+    else return BW_ERR_BAD_ARG;
+#undef BW_MG
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_moe_combine(const float* y, const int* pos_of, const float* wt, int top, int scale_output, float* out, int T,
+                             int H, int mode, const float* gain, float eps, void* stream) {
+    if (T <= 0) return 0;
+    if (mode < 0 || mode > 2 || (mode == 2 && !gain) || (size_t)H * sizeof(float) > 200 * 1024) return BW_ERR_BAD_ARG;
+    static bool raised[bw::MAX_DEVICES] = {};
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024 && bw::allow_dynamic_smem(moe_combine_kernel, 200 * 1024, raised) != cudaSuccess) return BW_ERR_DRIVER;
+    bw::launch((moe_combine_kernel), dim3(T), dim3(256), smem, (cudaStream_t)stream, y, pos_of, wt, top, scale_output, out, H, mode, gain, eps);
+    BW_LAUNCH_CHECK();
+    return 0;
+}

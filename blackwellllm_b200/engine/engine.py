@@ -276,6 +276,8 @@ class Engine:
             return None
         if not all(getattr(b.mixer, "graph_safe", True) for b in self.model.blocks):
             return None  # a mixer that works on the host between kernels cannot be captured
+        if getattr(self.model, "stream_hook", None) is not None:
+            return None  # someone looks at the stream layer by layer: nothing is replayed
         for e in entries:
             if len(e.tokens) != 1 or list(e.want) != [0]:
                 return None

@@ -284,13 +284,13 @@ def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.T
     return out
 
 
-def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int) -> torch.Tensor:
-    """cos and sin of ``pos * inv_freq`` per token: float32 [T, rotary_dim] (cos, then sin)."""
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, magnitude: float = 1.0) -> torch.Tensor:
+    """cos and sin of ``pos * inv_freq`` per token, times ``magnitude``: float32 [T, rotary_dim] (cos, then sin)."""
     _dev(positions, "positions", torch.int32); _dev(inv_freq, "inv_freq", torch.float32)
     T = positions.numel()
     table = torch.empty((T, rotary_dim), dtype=torch.float32, device=positions.device)
-    fn = _fn("elementwise", "bw_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(_ptr(positions), _ptr(inv_freq), _ptr(table), rotary_dim, T, _stream()), "rope_table")
+    fn = _fn("elementwise", "bw_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(positions), _ptr(inv_freq), _ptr(table), rotary_dim, T, float(magnitude), _stream()), "rope_table")
     return table
 
 
@@ -393,7 +393,7 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
 
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
                    req_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, window: Optional[int],
-                   scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   scale: float, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
     _dev(q, "q"); _dev(k_pages, "k_pages", q.dtype); _dev(v_pages, "v_pages", q.dtype)
     _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
     _dev(block_table, "block_table", torch.int32)
@@ -405,10 +405,10 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         out = torch.empty_like(q)
     fn = _fn("attention_simt", "bw_attention_simt",
              [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q, "q"), _ptr(positions), _ptr(req_of_token),
               _ptr(block_table), block_table.shape[1], _ptr(out), T, nh, nkv, hd, page_size, num_pages,
-              int(window or 0), float(scale), _stream()), "attention_simt")
+              int(window or 0), int(chunk or 0), float(scale), _stream()), "attention_simt")
     return out
 
 
@@ -674,22 +674,25 @@ def attention_takes_unrotated(hd: int, page_size: int) -> bool:
 
 
 def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
-                    block_table: torch.Tensor, nh: int, window: Optional[int], scale: float) -> torch.Tensor:
+                    block_table: torch.Tensor, nh: int, window: Optional[int], scale: float,
+                    chunk: Optional[int] = None) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
     holds this step's keys and values, unless ``q`` is an :class:`UnrotatedQKV`).  float32: the
-    CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size."""
+    CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size.  A query sees the keys
+    from ``first_visible(position, window, chunk)`` on: the latest ``window`` keys, and none before the
+    start of its own block of ``chunk`` positions (blocks are counted from position 0)."""
     if isinstance(q, UnrotatedQKV):
         if batch.T == batch.R and attention_takes_unrotated(k_pages.shape[3], k_pages.shape[2]):
-            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale)
+            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk)
         q = q.materialise()
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                              window, scale)
-    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale)
+                              window, scale, chunk=chunk)
+    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk)
 
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                   c_int, c_int, c_int, c_int, c_int, c_float,
+                                   c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                    c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
@@ -709,7 +712,7 @@ def num_sms(device=None) -> int:
 
 def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Optional[int], hd: int = 128,
                         rows_tile: int = 64, page_size: int = 16, static_bound: Optional[int] = None,
-                        sms: int = 148):
+                        sms: int = 148, chunk: Optional[int] = None):
     """The work lists of the tensor-core attention as plain lists (host arithmetic only):
     ``rows`` items (request, first token, 0, 0) for segments of more than 16 stacked rows (tokens x
     heads of a group), cut into tiles of ``rows_tile`` rows and ordered longest first; ``keys`` items
@@ -738,6 +741,8 @@ def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Option
         span = static_bound or kv_len[r]
         if window:
             span = min(span, window + n_q)
+        if chunk:   # a query sees no key before the start of its block of positions
+            span = min(span, chunk + n_q)
         tiles = -(-span // 64)
         n = max(1, min(want, tiles // 2, 64))
         keys_items += [(r, s, n, total_slices) for s in range(n)]
@@ -750,18 +755,18 @@ def plan_attention_work(q_len, q_start, kv_len, G: int, nkv: int, window: Option
 
 
 def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128, rows_tile: int = 64,
-                   page_size: int = 16):
+                   page_size: int = 16, chunk: Optional[int] = None):
     """The work lists of :func:`plan_attention_work` for this batch and group size on the device,
     made once per step and shared by all layers.  With ``batch.static_bound`` (graph replay) the
     number of key slices depends on that bound, not on the lengths."""
-    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size)
+    key = ("attn_work", G, nkv, window, hd, rows_tile, page_size, chunk)
     cached = batch.static_extras.get(key)
     if cached is not None:
         return cached
     R = batch.R
     rows_items, keys_items, merge_items, total_slices = plan_attention_work(
         batch.h_q_len[:R], batch.h_q_start[:R], batch.h_kv_len[:R], G, nkv, window, hd, rows_tile, page_size,
-        batch.static_bound, num_sms(batch.token_ids.device))
+        batch.static_bound, num_sms(batch.token_ids.device), chunk)
     dev = batch.token_ids.device
 
     def up(items):
@@ -776,7 +781,7 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
 
 
 def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
-                  nh: int, window: Optional[int], scale: float) -> torch.Tensor:
+                  nh: int, window: Optional[int], scale: float, chunk: Optional[int] = None) -> torch.Tensor:
     _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
@@ -805,7 +810,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     # prompt portions: the tcgen05 kernel (128-row tiles) where it takes the geometry, else mma.sync (64-row tiles)
     use_tc = attention_tc_supports(hd, G, page_size)
     rows_w, n_rows, keys_w, n_keys, merge_w, n_merge, slices, merge_max = attention_work(
-        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size)
+        batch, G, nkv, window, hd, rows_tile=128 if use_tc else 64, page_size=page_size, chunk=chunk)
     part_o = part_ml = None
     if n_merge:
         part_o = torch.empty((slices * nkv * 16, hd), dtype=torch.float32, device=out.device)
@@ -816,7 +821,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros=attention_tc_macros(hd))
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
                   _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
-                  nh, nkv, page_size, num_pages, int(window or 0), float(scale), _stream()), "attention_tc")
+                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _stream()), "attention_tc")
         n_rows = 0
         if not n_keys:
             return out
@@ -824,7 +829,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
               _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, _ptr(keys_w),
               n_keys, _ptr(merge_w), n_merge, _ptr(part_o), _ptr(part_ml), nh, nkv, page_size, num_pages,
-              int(window or 0), float(scale),
+              int(window or 0), int(chunk or 0), float(scale),
               _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
               raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
               raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, merge_max,
@@ -832,7 +837,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
     return out
 
 
-_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
 
 
 def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
@@ -883,3 +888,200 @@ def attention_tc_status() -> int:
 def _loaded_libs():
     from . import build
     return build._loaded
+
+
+# ------------------------------------------------------------------ norm after a sublayer, stream sums
+
+def rmsnorm_add(x: torch.Tensor, w: torch.Tensor, eps: float, stream: torch.Tensor) -> torch.Tensor:
+    """``stream += x / rms(x) * w`` row by row (float32 [T, H] both): the norm that follows a sublayer."""
+    _dev(x, "x", torch.float32); _dev(w, "w"); _dev(stream, "stream", torch.float32)
+    if x.shape != stream.shape or w.numel() != x.shape[-1]:
+        raise KernelError("rmsnorm_add: x and stream must be [T, H], the gain [H]")
+    fn = _fn("elementwise", "bw_rmsnorm_add", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _code(w, "w"), _ptr(stream), x.shape[0], x.shape[1], float(eps), _stream()), "rmsnorm_add")
+    return stream
+
+
+def add_into(target: torch.Tensor, other: torch.Tensor) -> torch.Tensor:
+    """``target += other`` (float32, same shape)."""
+    _dev(target, "target", torch.float32); _dev(other, "other", torch.float32)
+    if target.shape != other.shape:
+        raise KernelError("add_into: shapes differ")
+    fn = _fn("elementwise", "bw_add_planes", [c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p])
+    _check(fn(_ptr(target), _ptr(other), 1, other.numel(), target.numel(), _stream()), "add_planes")
+    return target
+
+
+# ------------------------------------------------------------------ q/k norm + rotation + append
+
+def qk_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, table: Optional[torch.Tensor],
+                        rotary_dim: int, interleaved: bool, q_gain: Optional[torch.Tensor],
+                        k_gain: Optional[torch.Tensor], eps: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                        nh: int, nkv: int, dq: int, dv: int, append: bool = True) -> torch.Tensor:
+    """``qkv`` float32 [T, nh*dq + nkv*dq + nkv*dv] -> queries [T, nh * dpad] in the pages' dtype, keys and
+    values to the pages [num_pages, nkv, page_size, dpad] of the tokens' positions (dpad >= dq, dv; the
+    channels beyond a head's own size are written as zeros).  With gains: all query channels of a token
+    are divided by their common root mean square and multiplied by ``q_gain`` (the same for the keys)
+    before the rotation.  ``table``: :func:`rope_table` of the step; ``interleaved``: channel 2i turns with
+    2i + 1, else channel i with i + rotary_dim / 2."""
+    _dev(qkv, "qkv", torch.float32); _dev(block_table, "block_table", torch.int32)
+    _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
+    T = qkv.shape[0]
+    num_pages, pk, page_size, dpad = k_pages.shape
+    if qkv.shape[1] != nh * dq + nkv * dq + nkv * dv or pk != nkv or v_pages.shape != k_pages.shape:
+        raise KernelError("qk_norm_rope_append: qkv must be [T, nh*dq + nkv*dq + nkv*dv], pages [num_pages, nkv, page, dpad]")
+    for name, g, n in (("q_gain", q_gain, nh * dq), ("k_gain", k_gain, nkv * dq)):
+        if g is not None:
+            _dev(g, name, torch.float32)
+            if g.numel() != n:
+                raise KernelError(f"qk_norm_rope_append: {name} must have {n} entries")
+    if rotary_dim:
+        _dev(table, "table", torch.float32)
+        if tuple(table.shape) != (T, rotary_dim):
+            raise KernelError("qk_norm_rope_append: the cos/sin table must be [T, rotary_dim]")
+    q_out = torch.empty((T, nh * dpad), dtype=k_pages.dtype, device=qkv.device)
+    fn = _fn("qk_norm_rope", "bw_qk_norm_rope_append",
+             [c_void_p] * 4 + [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p]
+             + [c_int] * 9 + [c_void_p])
+    _check(fn(_ptr(qkv), _ptr(batch.positions), _ptr(batch.req_of_token), _ptr(block_table), block_table.shape[1],
+              _ptr(table), int(rotary_dim), int(interleaved), _ptr(q_gain), _ptr(k_gain), float(eps), _ptr(q_out),
+              _ptr(k_pages), _ptr(v_pages), _code(k_pages, "pages"), T, nh, nkv, dq, dv, dpad, page_size,
+              num_pages if append else 0, _stream()), "qk_norm_rope_append")
+    return q_out
+
+
+# ------------------------------------------------------------------ gated linear attention
+
+GLA_MAX_KEY_DIM = 256
+
+
+def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Tensor, batch, state: torch.Tensor,
+             heads: int, dk: int, dv: int, q_scale: float, tau: float) -> torch.Tensor:
+    """The recurrence ``S <- diag(a) S + k v^T, o = S^T (q_scale q)`` with ``a = sigmoid(z) ** (1 / tau)`` over
+    the step's tokens, request by request in order, from and into ``state`` [slots, heads, dk, dv] (float32)
+    at the requests' slots.  ``proj`` float32 [T, ld] holds q, k, v at the given column offsets (head-major);
+    ``z`` float32 [T, heads * dk].  Returns o float32 [T, heads * dv]."""
+    _dev(proj, "proj", torch.float32); _dev(z, "z", torch.float32); _dev(state, "state", torch.float32)
+    T = proj.shape[0]
+    if dk > GLA_MAX_KEY_DIM:
+        raise KernelError(f"gla_scan: key size {dk} exceeds {GLA_MAX_KEY_DIM}")
+    if z.shape != (T, heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError("gla_scan: z must be [T, heads * dk], state [slots, heads, dk, dv]")
+    if max(q_off + heads * dk, k_off + heads * dk, v_off + heads * dv) > proj.shape[1]:
+        raise KernelError("gla_scan: q, k or v lie outside the projection's columns")
+    o = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    fn = _fn("gla", "bw_gla_scan", [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(z), _ptr(batch.cu_q), _ptr(batch.state_slot),
+              _ptr(state), _ptr(o), batch.R, heads, dk, dv, float(q_scale), float(tau), _stream()), "gla_scan")
+    return o
+
+
+def gla_gate(o: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.Tensor, heads: int, dv: int, eps: float,
+             out_dtype: torch.dtype) -> torch.Tensor:
+    """Per token and head ``o / rms(o) * gain * silu(g)`` with g at column ``g_off`` of ``proj``."""
+    _dev(o, "o", torch.float32); _dev(proj, "proj", torch.float32); _dev(gain, "gain", torch.float32)
+    T = o.shape[0]
+    if o.shape[1] != heads * dv or gain.numel() != dv or g_off + heads * dv > proj.shape[1]:
+        raise KernelError("gla_gate: o must be [T, heads * dv], the gain [dv], the gate inside the projection")
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
+    fn = _fn("gla", "bw_gla_gate", [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                    c_float, c_void_p])
+    _check(fn(_ptr(o), _ptr(proj), proj.stride(0), g_off, _ptr(gain), _ptr(out), _code(out, "out"), T, heads, dv,
+              float(eps), _stream()), "gla_gate")
+    return out
+
+
+# ------------------------------------------------------------------ routed feed-forward
+
+_moe_tile = None
+
+
+def moe_tile_rows() -> int:
+    """Rows of a tile of regrouped tokens (an expert's stretch of rows is padded to a multiple of it)."""
+    global _moe_tile
+    if _moe_tile is None:
+        _moe_tile = int(_fn("moe", "bw_moe_tile_rows", [])())
+    return _moe_tile
+
+
+def moe_max_tiles(rows: int, experts: int) -> int:
+    """Tiles that ``rows`` regrouped rows can take at most, whatever the routing."""
+    return -(-rows // moe_tile_rows()) + experts
+
+
+def moe_route(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False):
+    """float32 router logits [T, E] -> (chosen experts int32 [T, top], their weights float32 [T, top]):
+    scores are sigmoid(logit) (or the softmax over the experts), the ``top`` largest are chosen (lowest
+    index on ties) in falling order, optionally renormalised to sum 1."""
+    _dev(logits, "logits", torch.float32)
+    T, E = logits.shape
+    sel = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wt = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    fn = _fn("moe", "bw_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), T, E, int(top), int(softmax), int(renormalize), _ptr(sel), _ptr(wt), _stream()), "moe_route")
+    return sel, wt
+
+
+def moe_plan(sel: torch.Tensor, experts: int):
+    """(row of every (token, choice) in the regrouped order int32 [T * top], expert of every tile int32
+    [max_tiles], -1 for idle tiles)."""
+    _dev(sel, "sel", torch.int32)
+    n = sel.numel()
+    max_tiles = moe_max_tiles(n, experts)
+    pos_of = torch.empty(n, dtype=torch.int32, device=sel.device)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=sel.device)
+    fn = _fn("moe", "bw_moe_plan", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(sel), n, int(experts), max_tiles, _ptr(pos_of), _ptr(tile_expert), _stream()), "moe_plan")
+    return pos_of, tile_expert
+
+
+def moe_scatter(x: torch.Tensor, pos_of: torch.Tensor, wt: torch.Tensor, rows: int, scale_input: bool) -> torch.Tensor:
+    """The regrouped operand [rows, H]: row ``pos_of[t * top + k]`` = x[t] (times the choice's weight)."""
+    _dev(x, "x"); _dev(pos_of, "pos_of", torch.int32); _dev(wt, "wt", torch.float32)
+    T, H = x.shape
+    top = pos_of.numel() // max(T, 1)
+    xs = torch.empty((rows, H), dtype=x.dtype, device=x.device)
+    fn = _fn("moe", "bw_moe_scatter", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), _code(x, "x"), _ptr(pos_of), _ptr(wt), _ptr(xs), pos_of.numel(), H, top, int(scale_input), _stream()),
+           "moe_scatter")
+    return xs
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, w2: Optional[torch.Tensor] = None,
+             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Row r of the result is ``a[r] @ w[e].T`` with e the expert of r's tile; with ``w2`` it is
+    ``silu(a[r] @ w[e].T) * (a[r] @ w2[e].T)``.  a [rows, K], w (w2) [E, N, K]."""
+    _dev(a, "a"); _dev(w, "w", a.dtype); _dev(tile_expert, "tile_expert", torch.int32)
+    if w2 is not None:
+        _dev(w2, "w2", a.dtype)
+        if w2.shape != w.shape:
+            raise KernelError("moe_gemm: both weights must be [E, N, K]")
+    rows, K = a.shape
+    E, N, K2 = w.shape
+    if K != K2 or rows != tile_expert.numel() * moe_tile_rows():
+        raise KernelError("moe_gemm: a must be [tiles * tile rows, K], w [E, N, K]")
+    out = torch.empty((rows, N), dtype=out_dtype or a.dtype, device=a.device)
+    fn = _fn("moe", "bw_moe_gemm", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(w), _ptr(w2), _code(a, "a"), _ptr(tile_expert), _ptr(out), _code(out, "out"),
+              tile_expert.numel(), N, K, _stream()), "moe_gemm")
+    return out
+
+
+def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, wt: torch.Tensor, out: torch.Tensor, scale_output: bool,
+                mode: str = "write", gain: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
+    """``out[t]`` (= | +=) the sum over t's choices, in order, of (weight *) ``y[pos_of[t * top + k]]``;
+    mode "norm_add": the sum is divided by its root mean square, multiplied by ``gain`` and added."""
+    _dev(y, "y", torch.float32); _dev(pos_of, "pos_of", torch.int32); _dev(wt, "wt", torch.float32)
+    _dev(out, "out", torch.float32)
+    T, H = out.shape
+    modes = {"write": 0, "add": 1, "norm_add": 2}
+    if mode not in modes or y.shape[1] != H or (mode == "norm_add" and gain is None):
+        raise KernelError("moe_combine: bad mode or shapes")
+    if gain is not None:
+        gain = _dev(gain, "gain", torch.float32)
+    fn = _fn("moe", "bw_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                       c_float, c_void_p])
+    _check(fn(_ptr(y), _ptr(pos_of), _ptr(wt), pos_of.numel() // max(T, 1), int(scale_output), _ptr(out), T, H, modes[mode],
+              _ptr(gain), float(eps), _stream()), "moe_combine")
+    return out

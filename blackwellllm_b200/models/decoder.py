@@ -35,6 +35,10 @@ class DecoderModel:
                     raise ValueError(f"schedule entry {pos}: cache_of must name an earlier entry that owns its cache")
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
+        self._keeps_embedding = any(e.add_embedding for e in config.schedule)
+        # called as stream_hook(schedule position, stream [T, H] float32) after every run of a layer, if set:
+        # for looking at the stream layer by layer (the engine then runs uncaptured; see Engine.step)
+        self.stream_hook = None
 
     # ------------------------------------------------------------ parameters
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -78,12 +82,18 @@ class DecoderModel:
         c = self.config
         ops.discard_pending()   # nothing of an earlier (failed) pass is added into this one's tensors
         h = ops.embed_gather(self.embed, batch.token_ids, scale=c.embedding_multiplier)
+        h0 = h.clone() if self._keeps_embedding else None   # the embedding's output, for repeated passes
         for pos, e in enumerate(self.config.schedule):
             cache = caches[e.cache_of if e.cache_of is not None else pos]
             blk = self.blocks[e.layer]
-            if not blk.takes_pending:
+            if not blk.takes_pending or e.add_embedding:
                 ops.resolve_pending()   # the block before may have left its last sum to the next reader
+            if e.add_embedding:
+                ops.add_into(h, h0)
             blk.forward(h, batch, cache, owns_cache=e.cache_of is None)
+            if self.stream_hook is not None:
+                ops.resolve_pending()
+                self.stream_hook(pos, h)
         n = batch.logit_rows.numel()
         if n == 0:
             ops.discard_pending(h)

@@ -8,6 +8,15 @@ output projection added to the residual stream (bf16_linear_residual.cu:42-46).
 
 Here the three projections are one matrix (rows q, k, v) made at load, its result
 stays float32 until the rotation, and the residual sum is float32.
+
+Options of the spec beyond that: ``chunk`` (a query sees no key before the start of its own block of
+positions), ``v_head_dim`` (value size of a head other than its key size: the cache and the attention
+kernels run at the larger of the two, rounded up to what the kernels take, the rest zeros; the output
+projection's weight gets zero columns there), ``qk_norm_eps`` (an RMS norm over the whole query and the
+whole key projection before the rotation), an explicit ``softmax_scale``, and ``names`` for checkpoints
+that call the tensors otherwise.  With any of the first three, or an encoding that has no fused
+projection, the route is: projection (float32 out) -> one kernel that norms, rotates and appends
+(``PositionEncoding.norm_rotate_append``) -> attention -> output projection.
 """
 from __future__ import annotations
 
@@ -20,6 +29,11 @@ from .base import (BuildContext, Mixer, PagedKVRequest, ParamSpec, build_positio
 from .linear import Linear
 
 
+_DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                  "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+
+
 class GQAAttention(Mixer):
     def __init__(self, spec, hidden_size: int, ctx: BuildContext):
         self.nh, self.nkv, self.hd = int(spec.num_heads), int(spec.num_kv_heads), int(spec.head_dim)
@@ -28,48 +42,80 @@ class GQAAttention(Mixer):
         self.hidden_size = hidden_size
         self.qkv_bias = bool(spec.qkv_bias)
         self.window = spec.window
+        self.chunk = getattr(spec, "chunk", None)
+        self.dv = int(getattr(spec, "v_head_dim", None) or self.hd)
+        self.qk_norm_eps = getattr(spec, "qk_norm_eps", None)
+        self.names = dict(_DEFAULT_NAMES)
+        self.names.update(dict(getattr(spec, "names", ()) or ()))
+        # head size of the cache and the attention kernels: both sizes fit, in steps the kernels take
+        step = 16 if ctx.dtype == torch.bfloat16 else 1
+        self.dpad = -(-max(self.hd, self.dv) // step) * step
+        self.general = self.qk_norm_eps is not None or self.dv != self.hd or self.dpad != self.hd
+        self.q_gain = self.k_gain = None
         self.scale = float(spec.softmax_scale) if spec.softmax_scale is not None else self.hd ** -0.5
         self.ctx = ctx
         self.position = build_position(spec.position, self.hd, ctx)
-        ops.check_attention_supported(ctx.dtype, self.hd, self.nh // self.nkv)
+        ops.check_attention_supported(ctx.dtype, self.dpad, self.nh // self.nkv)
         self.qkv: Linear = None
         self.project = None
         self.o: Linear = None
 
     def cache_request(self):
-        return PagedKVRequest(self.nkv, self.hd, self.window)
+        return PagedKVRequest(self.nkv, self.dpad, self.window)
 
     def param_specs(self) -> List[ParamSpec]:
-        H, q, kv = self.hidden_size, self.nh * self.hd, self.nkv * self.hd
-        specs = [ParamSpec("q_proj.weight", (q, H)), ParamSpec("k_proj.weight", (kv, H)),
-                 ParamSpec("v_proj.weight", (kv, H)), ParamSpec("o_proj.weight", (H, q))]
+        H, q, k, v = self.hidden_size, self.nh * self.hd, self.nkv * self.hd, self.nkv * self.dv
+        n = self.names
+        specs = [ParamSpec(n["q"], (q, H)), ParamSpec(n["k"], (k, H)), ParamSpec(n["v"], (v, H)),
+                 ParamSpec(n["o"], (H, self.nh * self.dv))]
         if self.qkv_bias:
-            specs += [ParamSpec("q_proj.bias", (q,), role="bias", init="bias_normal"),
-                      ParamSpec("k_proj.bias", (kv,), role="bias", init="bias_normal"),
-                      ParamSpec("v_proj.bias", (kv,), role="bias", init="bias_normal")]
+            specs += [ParamSpec(n["q_bias"], (q,), role="bias", init="bias_normal"),
+                      ParamSpec(n["k_bias"], (k,), role="bias", init="bias_normal"),
+                      ParamSpec(n["v_bias"], (v,), role="bias", init="bias_normal")]
+        if self.qk_norm_eps is not None:
+            specs += [ParamSpec(n["q_norm"], (q,), role="gain", init="ones"),
+                      ParamSpec(n["k_norm"], (k,), role="gain", init="ones")]
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        w = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]], dim=0)
+        n = self.names
+        w = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0)
         b = None
         if self.qkv_bias:
-            bs = [tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]
+            bs = [tensors[n["q_bias"]], tensors[n["k_bias"]], tensors[n["v_bias"]]]
             dt = bs[0].dtype if all(t.dtype == bs[0].dtype for t in bs) else torch.float32
             b = torch.cat([t.to(dt) for t in bs], dim=0)
-        # an encoding that runs inside the projection takes the weight over; else project, then encode
-        self.project = self.position.fuse_projection(w, b, self.nh, self.nkv, self.hd)
+        wo = tensors[n["o"]]
+        if self.qk_norm_eps is not None:
+            self.q_gain = tensors[n["q_norm"]].float().contiguous()
+            self.k_gain = tensors[n["k_norm"]].float().contiguous()
+        if self.general:
+            if self.dpad != self.dv:   # the attention's output has dpad channels a head; those beyond dv are zeros
+                wo = torch.nn.functional.pad(wo.view(wo.shape[0], self.nh, self.dv), (0, self.dpad - self.dv)) \
+                    .reshape(wo.shape[0], self.nh * self.dpad)
+            self.project = None
+        else:
+            # an encoding that runs inside the projection takes the weight over; else project, then encode
+            self.project = self.position.fuse_projection(w, b, self.nh, self.nkv, self.hd)
         self.qkv = Linear(w, b) if self.project is None else None
-        self.o = Linear(tensors["o_proj.weight"])
+        self.o = Linear(wo)
 
-    def forward(self, x, residual, batch, cache, owns_cache: bool = True) -> None:
+    def forward(self, x, residual, batch, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         if self.project is not None:
             q = self.project(x, batch, cache, owns_cache)
         else:
             qkv = self.qkv(x, out_dtype=torch.float32)
-            q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
+            if self.general:
+                q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
+                                                     self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache)
+            else:
+                q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
         o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
-                                self.nh, self.window, self.scale)
-        self.o.add_to(o, residual)
+                                self.nh, self.window, self.scale, self.chunk)
+        if accumulate:
+            self.o.add_to(o, residual)
+        else:
+            self.o(o, out=residual)
 
 
 register_mixer("gqa_attention", GQAAttention)

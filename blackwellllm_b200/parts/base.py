@@ -16,6 +16,8 @@ Mixer           ``cache_request()`` says what cache it needs (paged keys/values,
                 ``forward(x, residual, batch, cache, owns_cache)`` adds its output
                 to ``residual`` (float32 [T,H]) in place; ``owns_cache`` is false
                 when this run reads the cache of another run and must not write it.
+                Mixers and feed-forwards that take ``accumulate=False`` WRITE their output to
+                ``residual`` instead (a block that norms the output before adding it needs that).
 FeedForward     ``forward(x, residual, batch)`` adds its output to ``residual``.
 Block           ``forward(residual, batch, cache)`` arranges norms, mixer and
                 feed-forward.
@@ -40,7 +42,8 @@ class ParamSpec:
     the compute dtype), ``"gain"`` / ``"bias"`` (vectors: a 32-bit stored tensor
     stays 32-bit), ``"int_table"`` (held as int32).  ``init``: how the
     random-weights mode fills it (``"normal"``, ``"ones"``, ``"bias_normal"``,
-    ``"zeros"``).
+    ``"zeros"``).  A size of -1 in ``shape`` is taken from the stored tensor (a size that the
+    configuration does not state); the random-weights mode cannot fill such a tensor.
     """
     name: str
     shape: Tuple[int, ...]
@@ -93,6 +96,13 @@ class PositionEncoding(Part):
     def rotate_append(self, qkv, batch, cache, nh: int, nkv: int, hd: int, append: bool = True) -> torch.Tensor:
         """qkv [T, (nh + 2 nkv) * hd] float32 -> encoded queries [T, nh * hd]; encoded keys and raw
         values are written to the cache when ``append``."""
+        raise NotImplementedError
+
+    def norm_rotate_append(self, qkv, batch, cache, nh: int, nkv: int, dq: int, dv: int, q_gain, k_gain, eps: float,
+                           append: bool = True) -> torch.Tensor:
+        """The general form of :meth:`rotate_append`: qkv [T, nh*dq + nkv*dq + nkv*dv] float32; with gains,
+        all query channels of a token (and all its key channels) are RMS-normed together first; the cache's
+        head size may exceed dq and dv (the rest is written as zeros)."""
         raise NotImplementedError
 
     def fuse_projection(self, weight: torch.Tensor, bias: Optional[torch.Tensor], nh: int, nkv: int, hd: int):

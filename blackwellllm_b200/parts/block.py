@@ -63,4 +63,43 @@ class PreNormBlock(Block):
             self.ffn.forward(x, residual, batch)
 
 
+class SandwichBlock(PreNormBlock):
+    """A norm before AND after each sublayer: ``x += post(mixer(pre(x)))``, ``x += post(ffn(pre(x)))``.  The
+    sublayer writes its output to a float32 buffer of its own (``accumulate=False``); the second norm reads
+    it and adds the result to the stream in one kernel.  A feed-forward with ``forward_post`` does the
+    second norm inside its own last kernel."""
+    takes_pending = False
+
+    def __init__(self, layer_spec, hidden_size: int, ctx: BuildContext):
+        super().__init__(layer_spec, hidden_size, ctx)
+        if layer_spec.mixer_post_norm is None or (layer_spec.ffn is not None and layer_spec.ffn_post_norm is None):
+            raise ValueError("the sandwich arrangement needs a norm after each sublayer")
+        self.mixer_post = build_norm(layer_spec.mixer_post_norm, hidden_size, ctx)
+        self.ffn_post = build_norm(layer_spec.ffn_post_norm, hidden_size, ctx) if self.ffn is not None else None
+        for norm in (self.mixer_post, self.ffn_post):
+            if norm is not None and not hasattr(norm, "add_to"):
+                raise ValueError(f"{type(norm).__name__} cannot follow a sublayer (it has no add_to)")
+
+    def _children(self):
+        s = self.spec
+        kids = super()._children() + [(s.mixer_post_norm_prefix, self.mixer_post)]
+        if self.ffn is not None:
+            kids.append((s.ffn_post_norm_prefix, self.ffn_post))
+        return kids
+
+    def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
+        x = self._normed(self.mixer_norm, residual)
+        branch = torch.empty_like(residual)
+        self.mixer.forward(x, branch, batch, cache, owns_cache, accumulate=False)
+        self.mixer_post.add_to(branch, residual)
+        if self.ffn is not None:
+            x = self.ffn_norm.forward(residual)
+            if hasattr(self.ffn, "forward_post"):
+                self.ffn.forward_post(x, residual, batch, self.ffn_post)
+            else:
+                self.ffn.forward(x, branch, batch, accumulate=False)
+                self.ffn_post.add_to(branch, residual)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("sandwich", SandwichBlock)

@@ -22,13 +22,18 @@ class RMSNorm(Norm):
         self.eps = float(spec.eps)
         self.hidden_size = hidden_size
         self.ctx = ctx
+        self.param = getattr(spec, "param", "weight")
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.hidden_size,), role="gain", init="ones")]
+        return [ParamSpec(self.param, (self.hidden_size,), role="gain", init="ones")]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.param].contiguous()
+
+    def add_to(self, x: torch.Tensor, stream: torch.Tensor) -> None:
+        """``stream += norm(x)`` (float32 both): the norm of a sublayer's output on its way into the stream."""
+        ops.rmsnorm_add(x, self.weight, self.eps, stream)
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.ctx.dtype, rows=rows)

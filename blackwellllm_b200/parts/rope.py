@@ -7,6 +7,12 @@ wavelength bands (src/kernels/rope.cuh:24-38).  The table is computed once on th
 host in float64 and stored as float32; the angle is the float32 product
 ``float(pos) * inv_freq[j]`` and sine/cosine are the precise ones.
 
+With ``interleaved`` the pair is (2j, 2j + 1); YaRN scaling (``rotary_inv_freq``,
+``rotary_magnitude``) rescales the frequencies by how often a pair turns within the original context
+and multiplies cosines and sines by a constant.  ``norm_rotate_append`` is the general route: an
+optional RMS norm over the whole query and the whole key projection, then the rotation, for heads whose
+value size may differ from their key size.
+
 :class:`NoPosition` rotates nothing.  Both append rotated keys and raw values to
 the cache pages in the same kernel.
 """
@@ -23,7 +29,16 @@ from .base import BuildContext, PositionEncoding, register_position
 def rotary_inv_freq(theta: float, rotary_dim: int, scaling=None) -> torch.Tensor:
     j = torch.arange(rotary_dim // 2, dtype=torch.float64)
     inv = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * j / rotary_dim)
-    if scaling is not None:
+    if scaling is not None and getattr(scaling, "kind", None) == "yarn":
+        # pairs that turn more than `fast` times within the original context keep their frequency, pairs
+        # that turn fewer than `slow` times have it divided by `factor`, a ramp over the pair index between
+        def pair_of(turns):
+            return rotary_dim * math.log(scaling.original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+        lo = max(math.floor(pair_of(scaling.fast)), 0)
+        hi = min(math.ceil(pair_of(scaling.slow)), rotary_dim - 1)
+        ramp = ((j - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        inv = inv / scaling.factor * ramp + inv * (1.0 - ramp)
+    elif scaling is not None:
         if getattr(scaling, "kind", None) != "llama3":
             raise ValueError(f"unknown rope scaling {scaling!r}")
         orig = float(scaling.original_max_position_embeddings)
@@ -36,12 +51,21 @@ def rotary_inv_freq(theta: float, rotary_dim: int, scaling=None) -> torch.Tensor
     return inv.to(torch.float32)
 
 
+def rotary_magnitude(scaling) -> float:
+    """The factor on every cosine and sine: 0.1 ln(factor) + 1 for YaRN, 1 otherwise."""
+    if scaling is not None and getattr(scaling, "kind", None) == "yarn":
+        return 0.1 * math.log(scaling.factor) + 1.0
+    return 1.0
+
+
 class RotaryEncoding(PositionEncoding):
     def __init__(self, spec, head_dim: int, ctx: BuildContext):
         if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= head_dim:
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be even and in (0, head_dim={head_dim}]")
         self.rotary_dim = int(spec.rotary_dim)
         self.inv_freq = rotary_inv_freq(spec.theta, self.rotary_dim, spec.scaling).to(ctx.device)
+        self.interleaved = bool(getattr(spec, "interleaved", False))
+        self.magnitude = rotary_magnitude(spec.scaling)
         self._key = ("rope_table", float(spec.theta), self.rotary_dim, spec.scaling)
 
     def _table(self, batch):
@@ -49,11 +73,18 @@ class RotaryEncoding(PositionEncoding):
         # rotary parameters: computed by the first one, kept on the batch for the others
         table = batch.extras.get(self._key)
         if table is None:
-            table = ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim)
+            table = ops.rope_table(batch.positions, self.inv_freq, self.rotary_dim, self.magnitude)
             batch.extras[self._key] = table
         return table
 
+    def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True):
+        return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
+                                       self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
+                                       dq, dv, append=append)
+
     def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
+        if self.interleaved or self.magnitude != 1.0:
+            return self.norm_rotate_append(qkv, batch, cache, nh, nkv, hd, hd, None, None, 0.0, append)
         table = self._table(batch)
         return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
                                self.inv_freq, self.rotary_dim, cache.k_pages, cache.v_pages, nh, nkv, hd,
@@ -64,6 +95,8 @@ class RotaryEncoding(PositionEncoding):
         # bfloat16 on the tensor-core product: rotation and append run in its epilogue
         if weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.shape[1] % 8:
             return None
+        if self.interleaved or self.magnitude != 1.0:
+            return None   # the fused epilogue turns channel i with i + rotary_dim / 2 and takes no magnitude
         order = ops.rotary_row_order(nh, nkv, hd, self.rotary_dim).to(weight.device)
         w = weight.index_select(0, order).contiguous()
         b = bias.index_select(0, order).contiguous() if bias is not None else None
@@ -105,6 +138,10 @@ class NoPosition(PositionEncoding):
     def rotate_append(self, qkv, batch, cache, nh, nkv, hd, append=True):
         return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
                                None, 0, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
+
+    def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True):
+        return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
+                                       eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, append=append)
 
 
 register_position("rope", RotaryEncoding)

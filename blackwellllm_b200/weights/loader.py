@@ -69,7 +69,8 @@ def check_names(where: str, expected: Mapping[str, ParamSpec], found: Mapping[st
     wrong_shape, wrong_type = [], []
     for n, s in expected.items():
         if n in found:
-            if tuple(found[n].shape) != tuple(s.shape):
+            got = tuple(found[n].shape)
+            if len(got) != len(s.shape) or any(w != -1 and w != g for w, g in zip(s.shape, got)):
                 wrong_shape.append((n, tuple(found[n].shape), tuple(s.shape)))
             dt = found[n].dtype
             if (s.role == "int_table" and dt not in _INTS) or (s.role != "int_table" and dt not in _FLOATS):

@@ -32,6 +32,9 @@ def random_tensors(specs: Mapping[str, ParamSpec], seed: int, std: float = 0.02,
         s = specs[name]
         if s.optional and skip_optional:
             continue
+        if any(d < 0 for d in s.shape):
+            raise ValueError(f"tensor {name!r}: the configuration leaves a size open ({list(s.shape)}); "
+                             f"the random-weights mode needs it stated")
         g = torch.Generator(device=device)
         g.manual_seed((int(seed) * 1_000_003 + idx) & 0x7FFF_FFFF_FFFF_FFFF)
         if s.init == "ones":
