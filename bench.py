@@ -303,6 +303,102 @@ def serve_workload(shape_key, steps_cap=None):
     return out
 
 
+# ------------------------------------------------------------------ a design beside its closest existing model
+def _gafulix_shape(width, heads, kv, hd, gla_heads, gla_dk, gla_dv, experts, top, ff, block, vocab, pairs):
+    """``pairs`` times (a gated-linear-attention layer, an attention layer), each with a routed feed-forward,
+    and the dense decoder of equal width, depth, heads and ACTIVE feed-forward size (top * ff)."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    gla = {"type": "gla", "mixer": {"heads": gla_heads, "dim": gla_dk, "vdim": gla_dv, "tau": 16.0, "rank": 16}, "mlp": moe}
+    att = {"type": "attention", "mlp": moe,
+           "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": block},
+                     "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}}
+    design = {"architecture": "Gafulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": [gla, att] * pairs}
+    dense = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width,
+             "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "intermediate_size": top * ff,
+             "num_hidden_layers": 2 * pairs, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-5}
+    return design, dense
+
+
+DESIGN_SHAPES = {
+    # width, heads, kv heads, head size, GLA heads, key size, value size, experts, top, expert size, mask block, vocab, layer pairs
+    "2k": (2048, 16, 4, 128, 8, 128, 256, 16, 2, 1024, 1024, 32000, 2),
+    "4k": (4096, 32, 8, 128, 16, 128, 256, 8, 2, 3584, 2048, 32000, 2),
+}
+
+
+def design_comparison(args):
+    """Prefill and decode throughput of the Gafulix design beside the dense decoder of equal size (random
+    bfloat16 weights), and where each spends a step: time per launcher of one uncaptured prefill step and one
+    uncaptured decode step, with what the design's own kernels reach of the measured peaks."""
+    import torch
+    from blackwellllm_b200 import Engine, StepEntry
+    from blackwellllm_b200.kernels import ops
+    pk = peaks()
+    T, B, C = args.prefill_tokens, args.batch, min(args.context, 2048)
+    out = {"workload": "design gafulix beside the dense decoder", "prefill_tokens": T, "decode_batch": B, "decode_context": C,
+           "peaks": pk, "sizes": {}}
+    gen = torch.Generator().manual_seed(7)
+    for key in [k for k in args.design_sizes.split(",") if k]:
+        design, dense = _gafulix_shape(*DESIGN_SHAPES[key])
+        V = design["vocab"]
+        row = {}
+        for label, cfg in (("gafulix", design), ("dense", dense)):
+            page = 16
+            eng = Engine.from_config(cfg, seed=3, std=0.02, dtype="bfloat16", page_size=page,
+                                     num_pages=(B + 1) * -(-(max(T, C) + args.steps + args.warmup + 64) // page),
+                                     max_requests=B + 1, max_batch_tokens=max(T, B * 256))
+            eng.options.graph_after = 1
+            prompt = torch.randint(0, V, (T,), generator=gen).tolist()
+
+            def prefill_step():
+                eng.step([StepEntry("p", prompt, [T - 1])])
+                eng.end_request("p")
+            times = []
+            for _ in range(args.warmup):
+                prefill_step()
+            for _ in range(3):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize(); s.record(); prefill_step(); e.record(); torch.cuda.synchronize()
+                times.append(s.elapsed_time(e))
+            ms_prefill = min(times)
+            ops.enable_timing(True)
+            prefill_step()
+            per_prefill = {k: round(v[1], 4) for k, v in sorted(ops.timing_report().items(), key=lambda kv: -kv[1][1])}
+            ops.enable_timing(False)
+            # decode: B requests with C tokens of context each, then one token each per step
+            for b in range(B):
+                ids = torch.randint(0, V, (C,), generator=gen).tolist()
+                for at in range(0, C, 512):
+                    eng.step([StepEntry(("d", b), ids[at:at + 512], [])])
+            nxt = torch.randint(0, V, (B,), generator=gen).tolist()
+
+            def decode_step():
+                return eng.step([StepEntry(("d", b), [nxt[b]], [0]) for b in range(B)])
+            for _ in range(args.warmup):
+                decode_step()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); s.record()
+            for _ in range(args.steps):
+                decode_step()
+            e.record(); torch.cuda.synchronize()
+            ms_decode = s.elapsed_time(e) / args.steps
+            graphs, eng.options.cuda_graphs = eng.options.cuda_graphs, False
+            ops.enable_timing(True)
+            decode_step()
+            per_decode = {k: round(v[1], 4) for k, v in sorted(ops.timing_report().items(), key=lambda kv: -kv[1][1])}
+            ops.enable_timing(False)
+            eng.options.cuda_graphs = graphs
+            row[label] = {"prefill_tokens_per_s": round(T / ms_prefill * 1e3), "prefill_ms": round(ms_prefill, 3),
+                          "decode_tokens_per_s": round(B / ms_decode * 1e3), "decode_ms": round(ms_decode, 4),
+                          "graph_launchers": eng.graph_kernel_count(B),
+                          "prefill_launcher_ms": per_prefill, "decode_launcher_ms": per_decode}
+            del eng
+            torch.cuda.empty_cache()
+        out["sizes"][key] = row
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -323,6 +419,9 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the JSON line then lacks the other part")
+    ap.add_argument("--design", default=None, choices=["gafulix"],
+                    help="instead of the default workload: this design beside the dense decoder of equal size")
+    ap.add_argument("--design-sizes", default="2k,4k", help="which of the design comparison's sizes to run")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -331,6 +430,8 @@ def main():
     if args.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {args.gpus} is not supported"}))
         return 2
+    if args.design is not None:
+        return design_comparison(args)
     if args.workload == "serve":
         if args.shape not in SERVE:
             print(json.dumps({"error": f"no serving workload for --shape {args.shape}; one of {sorted(SERVE)}"}))

@@ -6,11 +6,12 @@
 //
 //   moe_route    one warp per token: score = sigmoid(logit) (or softmax), the `top` largest scores
 //                (lowest index on ties), optionally renormalised to sum 1; float32 throughout
-//   moe_plan     one block: rows per expert, each expert's stretch padded to whole tiles of TILE_M rows,
+//   moe_plan     one block: rows per expert, each expert's stretch padded to whole tiles (64 rows here, 128 in moe_tc.cu),
 //                the place of every (token, choice) row, and the expert of every tile
 //   moe_scatter  the regrouped operand: row (token, choice) = weight * x[token] (input scaling) or x[token]
 //   moe_gemm     C[row, :] = A[row, :] W[expert of row]^T, optionally as silu(A Wg^T) * (A Wu^T);
-//                float32 sums on the CUDA cores from float32 or bfloat16 operands
+//                float32 sums on the CUDA cores from float32 or bfloat16 operands (the true 32-bit path, and
+//                bfloat16 sizes that the tcgen05 kernel of moe_tc.cu does not take)
 //   moe_combine  out[token] = sum over choices (in order) of (weight *) C[row of (token, choice)], written,
 //                added to a stream, or normalised (RMS, gain) and then added to a stream
 #include "common.cuh"
@@ -63,7 +64,7 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int so
 // ---------------------------------------------------------------- plan
 // pos_of[n] for the n = T * top rows (token-major); tile_expert[max_tiles] (-1: idle tile).
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ sel, int n, int E, int max_tiles, int* __restrict__ pos_of,
+moe_plan_kernel(const int* __restrict__ sel, int n, int E, int tile_rows, int max_tiles, int* __restrict__ pos_of,
                 int* __restrict__ tile_expert) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
@@ -79,7 +80,7 @@ moe_plan_kernel(const int* __restrict__ sel, int n, int E, int max_tiles, int* _
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
-        for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + TILE_M - 1) / TILE_M * TILE_M; }
+        for (int e = 0; e < E; ++e) { start[e] = at; at += (count[e] + tile_rows - 1) / tile_rows * tile_rows; }
         start[E] = at;
     }
     __syncthreads();
@@ -88,13 +89,13 @@ moe_plan_kernel(const int* __restrict__ sel, int n, int E, int max_tiles, int* _
         if (e >= 0 && e < E) pos_of[i] += start[e];
     }
     for (int tile = threadIdx.x; tile < max_tiles; tile += blockDim.x) {
-        const int row = tile * TILE_M;
+        const int row = tile * tile_rows;
         int e = -1;
         if (row < start[E]) {
             int lo = 0, hi = E - 1;            // the last expert whose stretch starts at or before row
             while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (start[mid] <= row) lo = mid; else hi = mid - 1; }
             e = lo;
-            if (row >= start[e] + count[e]) e = -1;   // wholly inside an expert's padding (cannot happen: padding < TILE_M)
+            if (row >= start[e] + count[e]) e = -1;   // wholly inside an expert's padding (cannot happen: the padding is less than a tile)
         }
         tile_expert[tile] = e;
     }
@@ -217,11 +218,12 @@ BW_EXPORT int bw_moe_route(const float* logits, int T, int E, int top, int softm
     return 0;
 }
 
-BW_EXPORT int bw_moe_plan(const int* sel, int n, int E, int max_tiles, int* pos_of, int* tile_expert, void* stream) {
+// tile_rows: rows of a tile (what the product kernel that follows works on); an expert's stretch is padded to it
+BW_EXPORT int bw_moe_plan(const int* sel, int n, int E, int tile_rows, int max_tiles, int* pos_of, int* tile_expert, void* stream) {
     if (n <= 0) return 0;
-    if (E <= 0 || E > 4096 || max_tiles < (n + TILE_M - 1) / TILE_M + E) return BW_ERR_BAD_ARG;
-    bw::launch((moe_plan_kernel), dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), (cudaStream_t)stream, sel, n, E, max_tiles,
-               pos_of, tile_expert);
+    if (E <= 0 || E > 4096 || tile_rows <= 0 || max_tiles < (n + tile_rows - 1) / tile_rows + E) return BW_ERR_BAD_ARG;
+    bw::launch((moe_plan_kernel), dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), (cudaStream_t)stream, sel, n, E, tile_rows,
+               max_tiles, pos_of, tile_expert);
     BW_LAUNCH_CHECK();
     return 0;
 }

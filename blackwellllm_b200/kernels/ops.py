@@ -1005,9 +1005,49 @@ def moe_tile_rows() -> int:
     return _moe_tile
 
 
-def moe_max_tiles(rows: int, experts: int) -> int:
+def moe_max_tiles(rows: int, experts: int, tile_rows: Optional[int] = None) -> int:
     """Tiles that ``rows`` regrouped rows can take at most, whatever the routing."""
-    return -(-rows // moe_tile_rows()) + experts
+    return -(-rows // (tile_rows or moe_tile_rows())) + experts
+
+
+_moe_tc_tile = None
+
+
+def moe_tc_tile_rows() -> int:
+    """Rows of a tile of the tcgen05 grouped product."""
+    global _moe_tc_tile
+    if _moe_tc_tile is None:
+        _moe_tc_tile = int(_fn("moe_tc", "bw_moe_tc_tile_rows", [])())
+    return _moe_tc_tile
+
+
+def moe_gemm_tc_supports(H: int, F: int) -> bool:
+    """Whether the tcgen05 grouped products take an expert of size F on width H (bfloat16): inner sizes that
+    are multiples of 8 (TMA rows), gate/up rows interleaved in blocks of 16.  BW_MOE_TC=0 keeps the CUDA cores."""
+    return os.environ.get("BW_MOE_TC", "1") != "0" and H % 8 == 0 and F % 16 == 0
+
+
+def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, gated: bool = False,
+                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """The grouped product on the tensor cores: a bfloat16 [tiles * 128, K], w bfloat16 [E, N, K]; row r gets
+    ``a[r] @ w[e].T`` with e the expert of r's tile.  ``gated``: w's rows alternate 16 gate rows / 16 up rows
+    (:func:`interleave_gate_up` per expert) and the result is bfloat16 [rows, N / 2] = silu(gate) * up."""
+    _dev(a, "a", torch.bfloat16); _dev(w, "w", torch.bfloat16); _dev(tile_expert, "tile_expert", torch.int32)
+    rows, K = a.shape
+    E, N, K2 = w.shape
+    if K != K2 or rows != tile_expert.numel() * moe_tc_tile_rows():
+        raise KernelError("moe_gemm_tc: a must be [tiles * 128, K], w [E, N, K]")
+    out_dtype = torch.bfloat16 if gated else (out_dtype or torch.bfloat16)
+    out = torch.empty((rows, N // 2 if gated else N), dtype=out_dtype, device=a.device)
+    fn = _fn("moe_tc", "bw_moe_gemm_tc", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), _ptr(w), int(gated), _ptr(tile_expert), _ptr(out), _code(out, "out"), tile_expert.numel(), E, N, K,
+              _stream()), "moe_gemm_tc")
+    return out
+
+
+def moe_tc_status() -> int:
+    """0 if no bounded wait of the tcgen05 grouped product ever gave up (synchronises the device)."""
+    return int(_fn("moe_tc", "bw_moe_tc_status", [])())
 
 
 def moe_route(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False):
@@ -1023,16 +1063,17 @@ def moe_route(logits: torch.Tensor, top: int, softmax: bool = False, renormalize
     return sel, wt
 
 
-def moe_plan(sel: torch.Tensor, experts: int):
-    """(row of every (token, choice) in the regrouped order int32 [T * top], expert of every tile int32
-    [max_tiles], -1 for idle tiles)."""
+def moe_plan(sel: torch.Tensor, experts: int, tile_rows: Optional[int] = None):
+    """(row of every (token, choice) in the regrouped order int32 [T * top], expert of every tile of
+    ``tile_rows`` rows int32 [max_tiles], -1 for idle tiles)."""
     _dev(sel, "sel", torch.int32)
     n = sel.numel()
-    max_tiles = moe_max_tiles(n, experts)
+    tile_rows = tile_rows or moe_tile_rows()
+    max_tiles = moe_max_tiles(n, experts, tile_rows)
     pos_of = torch.empty(n, dtype=torch.int32, device=sel.device)
     tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=sel.device)
-    fn = _fn("moe", "bw_moe_plan", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
-    _check(fn(_ptr(sel), n, int(experts), max_tiles, _ptr(pos_of), _ptr(tile_expert), _stream()), "moe_plan")
+    fn = _fn("moe", "bw_moe_plan", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(sel), n, int(experts), int(tile_rows), max_tiles, _ptr(pos_of), _ptr(tile_expert), _stream()), "moe_plan")
     return pos_of, tile_expert
 
 

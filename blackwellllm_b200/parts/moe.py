@@ -6,7 +6,8 @@
 
 The step's (token, choice) rows are regrouped by expert on the device (``csrc/moe.cu``): each expert's
 rows form a stretch padded to whole tiles, two grouped matrix products run over the tiles (the first
-with the gate's activation in its epilogue), and one kernel sums each token's rows back in the order of
+with the gate's activation in its epilogue; bfloat16: tcgen05 tensor cores, ``csrc/moe_tc.cu``; float32,
+and sizes that kernel does not take: CUDA cores), and one kernel sums each token's rows back in the order of
 its choices, so a token's result does not depend on what else is in the batch.  Nothing is read back to
 the host, so a decode step can be captured in a CUDA graph.
 
@@ -37,7 +38,8 @@ class RoutedFFN(FeedForward):
         self.router_name = spec.router_name
         self.stem, self.gate_name, self.up_name, self.down_name = spec.expert_names
         self.router: Linear = None
-        self.w_gate = self.w_up = self.w_down = None
+        self.w_gate = self.w_up = self.w_down = self.w_gate_up = None
+        self.tc = False
         self._post_gain = None
 
     def _expert(self, e: int, which: str) -> str:
@@ -54,17 +56,29 @@ class RoutedFFN(FeedForward):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.router = Linear(tensors[self.router_name])
         stack = lambda which: torch.stack([tensors[self._expert(e, which)] for e in range(self.E)]).contiguous()
-        self.w_gate, self.w_up, self.w_down = stack(self.gate_name), stack(self.up_name), stack(self.down_name)
+        self.w_down = stack(self.down_name)
+        self.tc = (self.w_down.dtype == torch.bfloat16 and self.w_down.is_cuda
+                   and ops.moe_gemm_tc_supports(self.hidden_size, self.F))
+        if self.tc:   # one gate/up tensor whose rows alternate in blocks of 16: the activation runs in the product's epilogue
+            self.w_gate_up = torch.stack([ops.interleave_gate_up(tensors[self._expert(e, self.gate_name)],
+                                                                 tensors[self._expert(e, self.up_name)])
+                                          for e in range(self.E)]).contiguous()
+        else:
+            self.w_gate, self.w_up = stack(self.gate_name), stack(self.up_name)
 
     def _experts(self, x):
         """(rows' results float32 [rows, H], place of every (token, choice), weights)"""
         logits = self.router(x, out_dtype=torch.float32)      # float32 sums of exact products
         sel, wt = ops.moe_route(logits, self.top, self.softmax, self.renormalize)
-        pos_of, tile_expert = ops.moe_plan(sel, self.E)
-        rows = tile_expert.numel() * ops.moe_tile_rows()
-        xs = ops.moe_scatter(x, pos_of, wt, rows, self.scale_input)
-        a = ops.moe_gemm(xs, self.w_gate, tile_expert, w2=self.w_up)
-        y = ops.moe_gemm(a, self.w_down, tile_expert, out_dtype=torch.float32)
+        tile = ops.moe_tc_tile_rows() if self.tc else ops.moe_tile_rows()
+        pos_of, tile_expert = ops.moe_plan(sel, self.E, tile)
+        xs = ops.moe_scatter(x, pos_of, wt, tile_expert.numel() * tile, self.scale_input)
+        if self.tc:
+            a = ops.moe_gemm_tc(xs, self.w_gate_up, tile_expert, gated=True)
+            y = ops.moe_gemm_tc(a, self.w_down, tile_expert, out_dtype=torch.float32)
+        else:
+            a = ops.moe_gemm(xs, self.w_gate, tile_expert, w2=self.w_up)
+            y = ops.moe_gemm(a, self.w_down, tile_expert, out_dtype=torch.float32)
         return y, pos_of, wt
 
     def forward(self, x, residual, batch, accumulate: bool = True) -> None:
