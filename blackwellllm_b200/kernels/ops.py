@@ -955,25 +955,41 @@ def qk_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, tab
 GLA_MAX_KEY_DIM = 256
 
 
-def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, z: torch.Tensor, batch, state: torch.Tensor,
-             heads: int, dk: int, dv: int, q_scale: float, tau: float) -> torch.Tensor:
-    """The recurrence ``S <- diag(a) S + k v^T, o = S^T (q_scale q)`` with ``a = sigmoid(z) ** (1 / tau)`` over
-    the step's tokens, request by request in order, from and into ``state`` [slots, heads, dk, dv] (float32)
-    at the requests' slots.  ``proj`` float32 [T, ld] holds q, k, v at the given column offsets (head-major);
-    ``z`` float32 [T, heads * dk].  Returns o float32 [T, heads * dv]."""
-    _dev(proj, "proj", torch.float32); _dev(z, "z", torch.float32); _dev(state, "state", torch.float32)
+def gla_decay(proj: torch.Tensor, x_off: int, w: torch.Tensor, b: torch.Tensor, tau: float) -> torch.Tensor:
+    """``sigmoid(x w.T + b) ** (1 / tau)`` in float32, x being ``rank`` columns of ``proj`` from ``x_off`` on
+    (w [C, rank], b [C]): the decay of every key channel of every token, float32 [T, C]."""
+    _dev(proj, "proj", torch.float32); _dev(w, "w"); _dev(b, "b", w.dtype)
+    T = proj.shape[0]
+    C, rank = w.shape
+    if x_off + rank > proj.shape[1] or b.numel() != C:
+        raise KernelError("gla_decay: the first projection lies outside proj, or the bias has the wrong size")
+    a = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    fn = _fn("gla", "bw_gla_decay", [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                                     c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), x_off, _ptr(w), _ptr(b), _code(w, "w"), _ptr(a), T, C, rank, float(tau), _stream()),
+           "gla_decay")
+    return a
+
+
+def gla_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor, batch, state: torch.Tensor,
+             heads: int, dk: int, dv: int, q_scale: float) -> torch.Tensor:
+    """The recurrence ``S <- diag(a) S + k v^T, o = S^T (q_scale q)`` over the step's tokens, request by request
+    in order, from and into ``state`` [slots, heads, dk, dv] (float32) at the requests' slots.  ``proj`` float32
+    [T, ld] holds q, k, v at the given column offsets (head-major); ``decay`` float32 [T, heads * dk] holds a
+    (:func:`gla_decay`).  Returns o float32 [T, heads * dv]."""
+    _dev(proj, "proj", torch.float32); _dev(decay, "decay", torch.float32); _dev(state, "state", torch.float32)
     T = proj.shape[0]
     if dk > GLA_MAX_KEY_DIM:
         raise KernelError(f"gla_scan: key size {dk} exceeds {GLA_MAX_KEY_DIM}")
-    if z.shape != (T, heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
-        raise KernelError("gla_scan: z must be [T, heads * dk], state [slots, heads, dk, dv]")
+    if decay.shape != (T, heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError("gla_scan: decay must be [T, heads * dk], state [slots, heads, dk, dv]")
     if max(q_off + heads * dk, k_off + heads * dk, v_off + heads * dv) > proj.shape[1]:
         raise KernelError("gla_scan: q, k or v lie outside the projection's columns")
     o = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
     fn = _fn("gla", "bw_gla_scan", [c_void_p, c_ll, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                    c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
-    _check(fn(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(z), _ptr(batch.cu_q), _ptr(batch.state_slot),
-              _ptr(state), _ptr(o), batch.R, heads, dk, dv, float(q_scale), float(tau), _stream()), "gla_scan")
+                                    c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(decay), _ptr(batch.cu_q), _ptr(batch.state_slot),
+              _ptr(state), _ptr(o), batch.R, heads, dk, dv, float(q_scale), _stream()), "gla_scan")
     return o
 
 

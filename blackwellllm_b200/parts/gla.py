@@ -11,7 +11,9 @@ from step to step; a step's tokens of a request are walked in order, so a single
 portion of a prompt are one code path (``csrc/gla.cu``).  The decay, its logarithm, the recurrence and the
 head norm are float32; the projections run in the compute dtype with float32 sums and float32 results.
 
-q, k, v and the gate are one matrix made at load, so the input is read once.
+q, k, v, the gate and the decay's first projection are one matrix made at load, so the input is read once;
+the decay's second projection (a small inner size), its sigmoid, the division of the logarithm by tau
+and the exponential are one float32 kernel.
 """
 from __future__ import annotations
 
@@ -41,9 +43,8 @@ class GatedLinearAttention(Mixer):
         self.ctx = ctx
         self.names = dict(_DEFAULT_NAMES)
         self.names.update(dict(getattr(spec, "names", ()) or ()))
-        self.qkvg: Linear = None
-        self.decay_in: Linear = None
-        self.decay_out: Linear = None
+        self.proj: Linear = None
+        self.decay_w = self.decay_b = None
         self.o: Linear = None
         self.gain = None
 
@@ -61,9 +62,10 @@ class GatedLinearAttention(Mixer):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
-        self.qkvg = Linear(torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]], tensors[n["g"]]], dim=0))
-        self.decay_in = Linear(tensors[n["decay_in"]])
-        self.decay_out = Linear(tensors[n["decay_out"]], tensors[n["decay_bias"]])
+        self.proj = Linear(torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]], tensors[n["g"]],
+                                      tensors[n["decay_in"]]], dim=0))
+        self.decay_w = tensors[n["decay_out"]].contiguous()
+        self.decay_b = tensors[n["decay_bias"]].to(self.decay_w.dtype).contiguous()
         self.o = Linear(tensors[n["o"]])
         self.gain = tensors[n["norm"]].float().contiguous()
 
@@ -71,10 +73,9 @@ class GatedLinearAttention(Mixer):
         if not owns_cache:
             raise ops.KernelError("gated linear attention: a run cannot read another run's state")
         K, V = self.heads * self.dk, self.heads * self.dv
-        proj = self.qkvg(x, out_dtype=torch.float32)                 # [T, q | k | v | g]
-        z = self.decay_out(self.decay_in(x), out_dtype=torch.float32)  # decay logits, bias added
-        o = ops.gla_scan(proj, 0, K, 2 * K, z, batch, cache.state, self.heads, self.dk, self.dv,
-                         self.dk ** -0.5, self.tau)
+        proj = self.proj(x, out_dtype=torch.float32)                 # [T, q | k | v | g | decay's first projection]
+        a = ops.gla_decay(proj, 2 * K + 2 * V, self.decay_w, self.decay_b, self.tau)
+        o = ops.gla_scan(proj, 0, K, 2 * K, a, batch, cache.state, self.heads, self.dk, self.dv, self.dk ** -0.5)
         y = ops.gla_gate(o, proj, 2 * K + V, self.gain, self.heads, self.dv, self.eps, self.ctx.dtype)
         if accumulate:
             self.o.add_to(y, residual)

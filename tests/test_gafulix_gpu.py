@@ -179,15 +179,21 @@ def test_gla_recurrence_and_state_carry(ops, heads, dk, dv):
         batch.state_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
         T = batch.T
         proj = rnd(T, 2 * K + 2 * V, seed=10 + launch)
-        z = rnd(T, K, seed=20 + launch, scale=4.0)          # decays from nearly 0 to nearly 1
-        o = ops.gla_scan(proj.to(DEV), 0, K, 2 * K, z.to(DEV), batch, state, heads, dk, dv, dk ** -0.5, tau)
+        rank = 5
+        x1, w2, b2 = rnd(T, rank, seed=30 + launch, scale=2.0), rnd(K, rank, seed=31), rnd(K, seed=32)
+        z = x1 @ w2.T + b2                                   # decays from nearly 0 to nearly 1
+        proj = torch.cat([proj, x1], dim=1)
+        a_dev = ops.gla_decay(proj.to(DEV), 2 * K + 2 * V, w2.to(DEV), b2.to(DEV), tau)
+        want_a = torch.sigmoid(x1.double() @ w2.double().T + b2.double()).pow(1.0 / tau)
+        assert float((a_dev.double().cpu() - want_a).abs().max()) < 1e-6
+        o = ops.gla_scan(proj.to(DEV), 0, K, 2 * K, a_dev, batch, state, heads, dk, dv, dk ** -0.5)
         y = ops.gla_gate(o, proj.to(DEV), 2 * K + V, gain.to(DEV), heads, dv, eps, torch.float32)
         t0 = 0
         for r, n in enumerate(q_lens):
             p = proj[t0:t0 + n].double()
             q = p[:, :K].view(n, heads, dk) * dk ** -0.5
             k, v = p[:, K:2 * K].view(n, heads, dk), p[:, 2 * K:2 * K + V].view(n, heads, dv)
-            g = p[:, 2 * K + V:]
+            g = p[:, 2 * K + V:2 * K + 2 * V]
             a = torch.sigmoid(z[t0:t0 + n].double()).pow(1.0 / tau).view(n, heads, dk)
             want = torch.zeros(n, heads, dv, dtype=torch.float64)
             for t in range(n):
@@ -399,14 +405,16 @@ def test_token_by_token_from_the_first_token(name, dtype):
 def test_portions(name, dtype, sizes):
     _, _, _, reqs, ref = model(name, dtype)
     eng = engine_for(name, dtype)
-    for rid in ("r2", "r4"):
+    rows = {}
+    for rid in ("r0", "r2", "r4"):
         ids, at, k, steps = reqs[rid], 0, 0, []
         while at < len(ids):
             n = min(sizes[k % len(sizes)], len(ids) - at)
             steps.append([(rid, ids[at:at + n], at)])
             at, k = at + n, k + 1
-        check_rows(run_steps(eng, steps), ref, dtype, f"portions {sizes}", routed(name))
+        rows.update(run_steps(eng, steps))
         eng.end_request(rid)
+    check_rows(rows, ref, dtype, f"portions {sizes}", routed(name))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
