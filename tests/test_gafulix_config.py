@@ -34,7 +34,7 @@ def test_description_follows_the_configuration():
     assert isinstance(looped.layers[0].mixer.position, NoPositionSpec) and looped.layers[0].mixer.chunk is None
 
 
-@pytest.mark.parametrize("raw", [tg.MIXED, tg.WIDE, tg.LOOPED])
+@pytest.mark.parametrize("raw", [c for c, _ in tg.CONFIGS.values()])
 def test_order_of_layer_runs(raw):
     cfg = parse_config(raw)
     assert [(e.layer, e.add_embedding) for e in cfg.schedule] == plain.layer_order(raw)

@@ -74,7 +74,24 @@ LOOPED = {
     "loop": {"start": 1, "stop": 2, "times": 4},
 }
 
-CONFIGS = {"mixed": (MIXED, 8), "wide": (WIDE, 16), "looped": (LOOPED, 32)}   # name -> (config, page size)
+# sizes that no kernel's fast form takes: a width that is no multiple of 8 (no TMA row: the CUDA-core products, in
+# bfloat16 too), an expert size that is no multiple of 16, three query heads on one kv head, key 24 / value 40
+ODD = {
+    "architecture": "Gafulix", "vocab": 77, "width": 50, "norm": {"eps": 3e-5},
+    "layers": [
+        _layer(_attn(3, 1, 24, 40, 0.21, {"base": 777.0, "dims": 24, "scaling": YARN_B}, 7), _moe(3, 2, 20)),
+        _layer(_gla(2, 20, 12, 5.0, 3), _moe(5, 5, 12)),
+    ],
+}
+# recurrent layers only: no page pool at all, state slots alone; both layers twice
+RECURRENT = {
+    "architecture": "Gafulix", "vocab": 90, "width": 32, "norm": {"eps": 1e-5},
+    "layers": [_layer(_gla(2, 16, 24, 3.0, 4), _moe(2, 2, 16)), _layer(_gla(4, 8, 8, 30.0, 2), None)],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
+
+# name -> (config, page size)
+CONFIGS = {"mixed": (MIXED, 8), "wide": (WIDE, 16), "looped": (LOOPED, 32), "odd": (ODD, 16), "recurrent": (RECURRENT, 16)}
 
 
 def make_tensors(raw, seed, std=0.08, bias_std=0.3, dtype=torch.bfloat16):
