@@ -85,8 +85,8 @@ ODD = {
 }
 # recurrent layers only: no page pool at all, state slots alone; both layers twice
 RECURRENT = {
-    "architecture": "Gafulix", "vocab": 90, "width": 32, "norm": {"eps": 1e-5},
-    "layers": [_layer(_gla(2, 16, 24, 3.0, 4), _moe(2, 2, 16)), _layer(_gla(4, 8, 8, 30.0, 2), None)],
+    "architecture": "Gafulix", "vocab": 90, "width": 72, "norm": {"eps": 1e-5},
+    "layers": [_layer(_gla(2, 16, 24, 3.0, 4), _moe(2, 1, 16)), _layer(_gla(4, 8, 8, 8.0, 2), None)],
     "loop": {"start": 0, "stop": 2, "times": 2},
 }
 
