@@ -304,20 +304,60 @@ __global__ void rope_append_kernel(const IT* __restrict__ qkv, const int* __rest
 }
 
 // ---------------------------------------------------------------- norm of a branch, added to the stream
-// stream[i] += x[i] * rsqrt(mean(x[i]^2) + eps) * w  (the norm that FOLLOWS a sublayer).  One block per row.
-template <typename WT>
+// stream[i] += x[i] * rsqrt(mean(x[i]^2) + eps) * w  (the norm that FOLLOWS a sublayer); with w2 also
+// out[i] = stream[i] * rsqrt(mean(stream[i]^2) + eps2) * w2, the norm BEFORE the next sublayer, in the same pass.
+// One block per row; the row is read once (16-byte loads when the width allows) and kept in shared memory.
+template <typename WT, typename OT, bool NEXT>
 __global__ void rmsnorm_add_kernel(const float* __restrict__ x, const WT* __restrict__ w, float* __restrict__ stream,
-                                   int H, float eps) {
+                                   const WT* __restrict__ w2, OT* __restrict__ out, int H, float eps, float eps2) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
+    extern __shared__ __align__(16) float row[];   // [H]: x, then the new stream values
     __shared__ float scratch[32];
     const float* xr = x + (size_t)blockIdx.x * H;
-    float* o = stream + (size_t)blockIdx.x * H;
+    float* sr = stream + (size_t)blockIdx.x * H;
+    const bool vec = (H & 3) == 0;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) { float v = xr[c]; ss = fmaf(v, v, ss); }
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+            const float4 v = load4(xr + c);
+            store4(row + c, v);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) { const float v = xr[c]; row[c] = v; ss = fmaf(v, v, ss); }
+    }
     ss = bw::block_sum(ss, scratch);
     const float r = rsqrtf(ss / (float)H + eps);
-    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] += xr[c] * r * bw::to_f32(w[c]);
+    float ss2 = 0.f;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {   // each thread reads back what it wrote
+            const float4 v = load4(row + c), g = load4(w + c);
+            float4 o = load4(sr + c);
+            o.x += v.x * r * g.x; o.y += v.y * r * g.y; o.z += v.z * r * g.z; o.w += v.w * r * g.w;
+            store4(sr + c, o);
+            if (NEXT) { store4(row + c, o); ss2 = fmaf(o.x, o.x, ss2); ss2 = fmaf(o.y, o.y, ss2); ss2 = fmaf(o.z, o.z, ss2); ss2 = fmaf(o.w, o.w, ss2); }
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float o = sr[c] + row[c] * r * bw::to_f32(w[c]);
+            sr[c] = o;
+            if (NEXT) { row[c] = o; ss2 = fmaf(o, o, ss2); }
+        }
+    }
+    if (NEXT) {
+        ss2 = bw::block_sum(ss2, scratch);
+        const float r2 = rsqrtf(ss2 / (float)H + eps2);
+        OT* o = out + (size_t)blockIdx.x * H;
+        if (vec) {
+            for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+                const float4 v = load4(row + c), g = load4(w2 + c);
+                store4(o + c, make_float4(v.x * r2 * g.x, v.y * r2 * g.y, v.z * r2 * g.z, v.w * r2 * g.w));
+            }
+        } else {
+            for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = bw::from_f32<OT>(row[c] * r2 * bw::to_f32(w2[c]));
+        }
+    }
 }
 
 // ---------------------------------------------------------------- logits
@@ -406,17 +446,40 @@ BW_EXPORT int bw_add_rmsnorm(float* x, const float* planes, int n_planes, long l
 }
 
 // x[total] += the planes, added in plane order
+namespace {
+template <typename WT, typename OT, bool NEXT>
+int launch_rmsnorm_add(const float* x, const void* w, float* stream_rows, const void* w2, void* out, int n, int H, float eps,
+                       float eps2, cudaStream_t s) {
+    static bool raised[bw::MAX_DEVICES] = {};
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024 && bw::allow_dynamic_smem(rmsnorm_add_kernel<WT, OT, NEXT>, 200 * 1024, raised) != cudaSuccess) return BW_ERR_DRIVER;
+    const int threads = H >= 2048 ? 256 : 128;
+    bw::launch((rmsnorm_add_kernel<WT, OT, NEXT>), dim3(n), dim3(threads), smem, s, x, (const WT*)w, stream_rows, (const WT*)w2, (OT*)out, H, eps, eps2);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+}  // namespace
+
 BW_EXPORT int bw_rmsnorm_add(const float* x, const void* w, int w_type, float* stream_rows, int n, int H, float eps,
                              void* stream) {
     if (n <= 0) return 0;
-    if (H <= 0) return BW_ERR_BAD_ARG;
-    const int threads = H >= 1024 ? 256 : 128;
+    if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return BW_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (w_type == BW_F32) bw::launch((rmsnorm_add_kernel<float>), dim3(n), dim3(threads), 0, s, x, (const float*)w, stream_rows, H, eps);
-    else if (w_type == BW_BF16) bw::launch((rmsnorm_add_kernel<bf16>), dim3(n), dim3(threads), 0, s, x, (const bf16*)w, stream_rows, H, eps);
-    else return BW_ERR_BAD_ARG;
-    BW_LAUNCH_CHECK();
-    return 0;
+    if (w_type == BW_F32) return launch_rmsnorm_add<float, float, false>(x, w, stream_rows, nullptr, nullptr, n, H, eps, 0.f, s);
+    if (w_type == BW_BF16) return launch_rmsnorm_add<bf16, bf16, false>(x, w, stream_rows, nullptr, nullptr, n, H, eps, 0.f, s);
+    return BW_ERR_BAD_ARG;
+}
+
+// both gains of w_type; out of out_type
+BW_EXPORT int bw_rmsnorm_add_norm(const float* x, const void* w, float* stream_rows, const void* w2, int w_type, void* out,
+                                  int out_type, int n, int H, float eps, float eps2, void* stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (w_type == BW_F32 && out_type == BW_F32) return launch_rmsnorm_add<float, float, true>(x, w, stream_rows, w2, out, n, H, eps, eps2, s);
+    if (w_type == BW_F32 && out_type == BW_BF16) return launch_rmsnorm_add<float, bf16, true>(x, w, stream_rows, w2, out, n, H, eps, eps2, s);
+    if (w_type == BW_BF16 && out_type == BW_BF16) return launch_rmsnorm_add<bf16, bf16, true>(x, w, stream_rows, w2, out, n, H, eps, eps2, s);
+    return BW_ERR_BAD_ARG;
 }
 
 BW_EXPORT int bw_add_planes(float* x, const float* planes, int n_planes, long long plane_stride, long long total,

@@ -92,11 +92,17 @@ gla_scan_kernel(ScanParams p) {
     float* S = p.state + (((size_t)p.state_slot[r] * p.heads + h) * p.dk) * p.dv;
     BW_PDL_WAIT();
     float s[RPL][CPT];
+    const bool vec_state = (p.dv & 3) == 0 && cbase + CPT <= p.dv;   // a lane's CPT columns of a row as one 16-byte access
 #pragma unroll
     for (int j = 0; j < RPL; ++j) {
         const int i = ((j >> 2) * 32 + lane) * 4 + (j & 3);
+        if (vec_state) {
+            const float4 v = i < p.dk ? *reinterpret_cast<const float4*>(S + (size_t)i * p.dv + cbase) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s[j][0] = v.x; s[j][1] = v.y; s[j][2] = v.z; s[j][3] = v.w;
+        } else {
 #pragma unroll
-        for (int cc = 0; cc < CPT; ++cc) s[j][cc] = (i < p.dk && cbase + cc < p.dv) ? S[(size_t)i * p.dv + cbase + cc] : 0.f;
+            for (int cc = 0; cc < CPT; ++cc) s[j][cc] = (i < p.dk && cbase + cc < p.dv) ? S[(size_t)i * p.dv + cbase + cc] : 0.f;
+        }
     }
     // The next chunk's values travel from memory into registers while this chunk is worked on from shared
     // memory, so that their latency is not added to the chain through the tokens.
@@ -172,9 +178,13 @@ gla_scan_kernel(ScanParams p) {
 #pragma unroll
     for (int j = 0; j < RPL; ++j) {
         const int i = ((j >> 2) * 32 + lane) * 4 + (j & 3);
+        if (vec_state) {
+            if (i < p.dk) *reinterpret_cast<float4*>(S + (size_t)i * p.dv + cbase) = make_float4(s[j][0], s[j][1], s[j][2], s[j][3]);
+        } else {
 #pragma unroll
-        for (int cc = 0; cc < CPT; ++cc)
-            if (i < p.dk && cbase + cc < p.dv) S[(size_t)i * p.dv + cbase + cc] = s[j][cc];
+            for (int cc = 0; cc < CPT; ++cc)
+                if (i < p.dk && cbase + cc < p.dv) S[(size_t)i * p.dv + cbase + cc] = s[j][cc];
+        }
     }
 }
 

@@ -23,14 +23,35 @@ namespace {
 constexpr int TILE_M = 64;   // rows of a tile of regrouped tokens; also the padding of an expert's stretch
 constexpr int BN = 64, BK = 16;
 
+// dst[c] = src[c] * w over a row of H elements, thread `me` of `n`; 16-byte accesses when the row allows
+__device__ __forceinline__ void scale_row(const float* __restrict__ src, float* __restrict__ dst, int H, float w, int me, int n) {
+    if ((H & 3) == 0) {
+        for (int c = me * 4; c < H; c += n * 4) {
+            float4 v = *reinterpret_cast<const float4*>(src + c);
+            v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+            *reinterpret_cast<float4*>(dst + c) = v;
+        }
+    } else {
+        for (int c = me; c < H; c += n) dst[c] = src[c] * w;
+    }
+}
+__device__ __forceinline__ void scale_row(const bf16* __restrict__ src, bf16* __restrict__ dst, int H, float w, int me, int n) {
+    if ((H & 7) == 0) {
+        for (int c = me * 8; c < H; c += n * 8) {
+            uint4 raw = *reinterpret_cast<const uint4*>(src + c);
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); h[k] = __floats2bfloat162_rn(f.x * w, f.y * w); }
+            *reinterpret_cast<uint4*>(dst + c) = raw;
+        }
+    } else {
+        for (int c = me; c < H; c += n) dst[c] = __float2bfloat16_rn(__bfloat162float(src[c]) * w);
+    }
+}
+
 // ---------------------------------------------------------------- routing
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int softmax, int renorm,
-                 int* __restrict__ sel, float* __restrict__ wt) {
-    BW_PDL_TRIGGER();
-    BW_PDL_WAIT();
-    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (t >= T) return;
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int t, int lane, int E, int top, int softmax,
+                                            int renorm, int* __restrict__ sel, float* __restrict__ wt) {
     const float* z = logits + (size_t)t * E;
     float zmax = -INFINITY, zsum = 0.f;
     if (softmax) {
@@ -61,14 +82,20 @@ moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int so
         for (int k = 0; k < top; ++k) wt[(size_t)t * top + k] /= total;
 }
 
-// ---------------------------------------------------------------- plan
-// pos_of[n] for the n = T * top rows (token-major); tile_expert[max_tiles] (-1: idle tile).
-__global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ sel, int n, int E, int tile_rows, int max_tiles, int* __restrict__ pos_of,
-                int* __restrict__ tile_expert) {
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int softmax, int renorm,
+                 int* __restrict__ sel, float* __restrict__ wt) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
-    extern __shared__ int sh[];
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    route_token(logits, t, lane, E, top, softmax, renorm, sel, wt);
+}
+
+// ---------------------------------------------------------------- plan
+// pos_of[n] for the n = T * top rows (token-major); tile_expert[max_tiles] (-1: idle tile).
+__device__ __forceinline__ void plan_block(const int* __restrict__ sel, int n, int E, int tile_rows, int max_tiles,
+                                           int* __restrict__ pos_of, int* __restrict__ tile_expert, int* sh) {
     int* count = sh;          // [E]
     int* start = sh + E;      // [E + 1], in rows
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
@@ -101,6 +128,39 @@ moe_plan_kernel(const int* __restrict__ sel, int n, int E, int tile_rows, int ma
     }
 }
 
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ sel, int n, int E, int tile_rows, int max_tiles, int* __restrict__ pos_of,
+                int* __restrict__ tile_expert) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    extern __shared__ int sh[];
+    plan_block(sel, n, E, tile_rows, max_tiles, pos_of, tile_expert, sh);
+}
+
+// The three steps above as one block, for steps of few tokens (a decode step): choice, plan and regrouped operand
+// without two more launches.  The block's own writes to sel, wt and pos_of are read back after a barrier.
+template <typename XT>
+__global__ void __launch_bounds__(1024)
+moe_route_plan_scatter_kernel(const float* __restrict__ logits, int T, int E, int top, int softmax, int renorm,
+                              int* __restrict__ sel, float* __restrict__ wt, int tile_rows, int max_tiles,
+                              int* __restrict__ pos_of, int* __restrict__ tile_expert, const XT* __restrict__ x,
+                              XT* __restrict__ xs, int H, int scale_input) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    extern __shared__ int sh[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int t = warp; t < T; t += 32) route_token(logits, t, lane, E, top, softmax, renorm, sel, wt);
+    __syncthreads();
+    plan_block(sel, T * top, E, tile_rows, max_tiles, pos_of, tile_expert, sh);
+    __syncthreads();
+    for (int i = warp; i < T * top; i += 32) {
+        const float w = scale_input ? wt[i] : 1.f;
+        const XT* src = x + (size_t)(i / top) * H;
+        XT* dst = xs + (size_t)pos_of[i] * H;
+        scale_row(src, dst, H, w, lane, 32);
+    }
+}
+
 // ---------------------------------------------------------------- scatter
 template <typename XT>
 __global__ void __launch_bounds__(256)
@@ -113,7 +173,7 @@ moe_scatter_kernel(const XT* __restrict__ x, const int* __restrict__ pos_of, con
     const float w = scale_input ? wt[i] : 1.f;
     const XT* src = x + (size_t)t * H;
     XT* dst = xs + (size_t)pos_of[i] * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) dst[c] = bw::from_f32<XT>(bw::to_f32(src[c]) * w);
+    scale_row(src, dst, H, w, threadIdx.x, blockDim.x);
 }
 
 // ---------------------------------------------------------------- grouped product
@@ -181,27 +241,53 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, 
                    const float* __restrict__ gain, float eps) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
-    extern __shared__ float row[];    // [H]
+    extern __shared__ __align__(16) float row[];    // [H]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float v = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const float w = scale_output ? wt[(size_t)t * top + k] : 1.f;
-            v = fmaf(w, y[(size_t)pos_of[(size_t)t * top + k] * H + c], v);
+    const bool vec = (H & 3) == 0;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float w = scale_output ? wt[(size_t)t * top + k] : 1.f;
+                const float4 a = *reinterpret_cast<const float4*>(y + (size_t)pos_of[(size_t)t * top + k] * H + c);
+                v.x = fmaf(w, a.x, v.x); v.y = fmaf(w, a.y, v.y); v.z = fmaf(w, a.z, v.z); v.w = fmaf(w, a.w, v.w);
+            }
+            *reinterpret_cast<float4*>(row + c) = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
         }
-        row[c] = v;
-        ss = fmaf(v, v, ss);
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            float v = 0.f;
+            for (int k = 0; k < top; ++k) {
+                const float w = scale_output ? wt[(size_t)t * top + k] : 1.f;
+                v = fmaf(w, y[(size_t)pos_of[(size_t)t * top + k] * H + c], v);
+            }
+            row[c] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     float r = 1.f;
     if (mode == 2) r = rsqrtf(bw::block_sum(ss, scratch) / (float)H + eps);
     float* o = out + (size_t)t * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {   // each thread reads back what it wrote
-        const float v = row[c];
-        if (mode == 0) o[c] = v;
-        else if (mode == 1) o[c] += v;
-        else o[c] += v * r * gain[c];
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {   // each thread reads back what it wrote
+            const float4 v = *reinterpret_cast<const float4*>(row + c);
+            float4 d = mode == 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(o + c);
+            if (mode == 2) {
+                const float4 g = *reinterpret_cast<const float4*>(gain + c);
+                d.x += v.x * r * g.x; d.y += v.y * r * g.y; d.z += v.z * r * g.z; d.w += v.w * r * g.w;
+            } else { d.x += v.x; d.y += v.y; d.z += v.z; d.w += v.w; }
+            *reinterpret_cast<float4*>(o + c) = d;
+        }
+    } else {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) {
+            const float v = row[c];
+            if (mode == 0) o[c] = v;
+            else if (mode == 1) o[c] += v;
+            else o[c] += v * r * gain[c];
+        }
     }
 }
 
@@ -235,6 +321,25 @@ BW_EXPORT int bw_moe_scatter(const void* x, int type, const int* pos_of, const f
     if (type == BW_F32) bw::launch((moe_scatter_kernel<float>), dim3(n), dim3(256), 0, s, (const float*)x, pos_of, wt, (float*)xs, H, top, scale_input);
     else if (type == BW_BF16) bw::launch((moe_scatter_kernel<bf16>), dim3(n), dim3(256), 0, s, (const bf16*)x, pos_of, wt, (bf16*)xs, H, top, scale_input);
     else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_moe_route_plan_scatter(const float* logits, int T, int E, int top, int softmax, int renorm, int* sel, float* wt,
+                                        int tile_rows, int max_tiles, int* pos_of, int* tile_expert, const void* x, int type,
+                                        void* xs, int H, int scale_input, void* stream) {
+    if (T <= 0) return 0;
+    const int n = T * top;
+    if (E <= 0 || E > 4096 || top <= 0 || top > E || n > 1024 || tile_rows <= 0 || max_tiles < (n + tile_rows - 1) / tile_rows + E)
+        return BW_ERR_BAD_ARG;
+    const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
+    cudaStream_t s = (cudaStream_t)stream;
+#define BW_RPS(XT) bw::launch((moe_route_plan_scatter_kernel<XT>), dim3(1), dim3(1024), smem, s, logits, T, E, top, softmax, renorm, sel, wt, \
+        tile_rows, max_tiles, pos_of, tile_expert, (const XT*)x, (XT*)xs, H, scale_input)
+    if (type == BW_F32) BW_RPS(float);
+    else if (type == BW_BF16) BW_RPS(bf16);
+    else return BW_ERR_BAD_ARG;
+#undef BW_RPS
     BW_LAUNCH_CHECK();
     return 0;
 }

@@ -902,6 +902,21 @@ def rmsnorm_add(x: torch.Tensor, w: torch.Tensor, eps: float, stream: torch.Tens
     return stream
 
 
+def rmsnorm_add_norm(x: torch.Tensor, w: torch.Tensor, eps: float, stream: torch.Tensor, w_next: torch.Tensor,
+                     eps_next: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``stream += x / rms(x) * w`` and, in the same kernel, the next norm of the new stream:
+    returns ``stream / rms(stream) * w_next`` in ``out_dtype``."""
+    _dev(x, "x", torch.float32); _dev(w, "w"); _dev(stream, "stream", torch.float32); _dev(w_next, "w_next", w.dtype)
+    if x.shape != stream.shape or w.numel() != x.shape[-1] or w_next.numel() != x.shape[-1]:
+        raise KernelError("rmsnorm_add_norm: x and stream must be [T, H], the gains [H]")
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    fn = _fn("elementwise", "bw_rmsnorm_add_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                                    c_float, c_float, c_void_p])
+    _check(fn(_ptr(x), _ptr(w), _ptr(stream), _ptr(w_next), _code(w, "w"), _ptr(out), _code(out, "out"), x.shape[0], x.shape[1],
+              float(eps), float(eps_next), _stream()), "rmsnorm_add_norm")
+    return out
+
+
 def add_into(target: torch.Tensor, other: torch.Tensor) -> torch.Tensor:
     """``target += other`` (float32, same shape)."""
     _dev(target, "target", torch.float32); _dev(other, "other", torch.float32)
@@ -1077,6 +1092,34 @@ def moe_route(logits: torch.Tensor, top: int, softmax: bool = False, renormalize
     fn = _fn("moe", "bw_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(logits), T, E, int(top), int(softmax), int(renormalize), _ptr(sel), _ptr(wt), _stream()), "moe_route")
     return sel, wt
+
+
+MOE_FUSED_FRONT_MAX_ROWS = 128   # up to this many (token, choice) rows one block routes, plans and regroups (the kernel takes 1,024)
+
+
+def moe_route_plan_scatter(logits: torch.Tensor, x: torch.Tensor, top: int, tile_rows: int, softmax: bool = False,
+                           renormalize: bool = False, scale_input: bool = False):
+    """:func:`moe_route`, :func:`moe_plan` and :func:`moe_scatter` as one kernel, for steps of few tokens.
+    Returns (weights [T, top], place of every (token, choice), expert of every tile, the regrouped operand)."""
+    _dev(logits, "logits", torch.float32); _dev(x, "x")
+    T, E = logits.shape
+    H = x.shape[1]
+    n = T * top
+    if n > MOE_FUSED_FRONT_MAX_ROWS or x.shape[0] != T:
+        raise KernelError("moe_route_plan_scatter: too many rows for one block, or x and logits disagree")
+    max_tiles = moe_max_tiles(n, E, tile_rows)
+    dev = logits.device
+    sel = torch.empty((T, top), dtype=torch.int32, device=dev)
+    wt = torch.empty((T, top), dtype=torch.float32, device=dev)
+    pos_of = torch.empty(n, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    xs = torch.empty((max_tiles * tile_rows, H), dtype=x.dtype, device=dev)
+    fn = _fn("moe", "bw_moe_route_plan_scatter", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(logits), T, E, int(top), int(softmax), int(renormalize), _ptr(sel), _ptr(wt), int(tile_rows), max_tiles,
+              _ptr(pos_of), _ptr(tile_expert), _ptr(x), _code(x, "x"), _ptr(xs), H, int(scale_input), _stream()),
+           "moe_route_plan_scatter")
+    return wt, pos_of, tile_expert, xs
 
 
 def moe_plan(sel: torch.Tensor, experts: int, tile_rows: Optional[int] = None):

@@ -91,9 +91,15 @@ class SandwichBlock(PreNormBlock):
         x = self._normed(self.mixer_norm, residual)
         branch = torch.empty_like(residual)
         self.mixer.forward(x, branch, batch, cache, owns_cache, accumulate=False)
-        self.mixer_post.add_to(branch, residual)
-        if self.ffn is not None:
-            x = self.ffn_norm.forward(residual)
+        if self.ffn is None:
+            self.mixer_post.add_to(branch, residual)
+        else:
+            # the norm after the mixer and the norm before the feed-forward read the same row: one kernel if they can
+            if hasattr(self.mixer_post, "add_to_then"):
+                x = self.mixer_post.add_to_then(branch, residual, self.ffn_norm)
+            else:
+                self.mixer_post.add_to(branch, residual)
+                x = self.ffn_norm.forward(residual)
             if hasattr(self.ffn, "forward_post"):
                 self.ffn.forward_post(x, residual, batch, self.ffn_post)
             else:

@@ -69,10 +69,14 @@ class RoutedFFN(FeedForward):
     def _experts(self, x):
         """(rows' results float32 [rows, H], place of every (token, choice), weights)"""
         logits = self.router(x, out_dtype=torch.float32)      # float32 sums of exact products
-        sel, wt = ops.moe_route(logits, self.top, self.softmax, self.renormalize)
         tile = ops.moe_tc_tile_rows() if self.tc else ops.moe_tile_rows()
-        pos_of, tile_expert = ops.moe_plan(sel, self.E, tile)
-        xs = ops.moe_scatter(x, pos_of, wt, tile_expert.numel() * tile, self.scale_input)
+        if x.shape[0] * self.top <= ops.MOE_FUSED_FRONT_MAX_ROWS:     # few tokens (a decode step): one kernel
+            wt, pos_of, tile_expert, xs = ops.moe_route_plan_scatter(logits, x, self.top, tile, self.softmax,
+                                                                     self.renormalize, self.scale_input)
+        else:
+            sel, wt = ops.moe_route(logits, self.top, self.softmax, self.renormalize)
+            pos_of, tile_expert = ops.moe_plan(sel, self.E, tile)
+            xs = ops.moe_scatter(x, pos_of, wt, tile_expert.numel() * tile, self.scale_input)
         if self.tc:
             a = ops.moe_gemm_tc(xs, self.w_gate_up, tile_expert, gated=True)
             y = ops.moe_gemm_tc(a, self.w_down, tile_expert, out_dtype=torch.float32)

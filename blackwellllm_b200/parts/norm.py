@@ -35,6 +35,13 @@ class RMSNorm(Norm):
         """``stream += norm(x)`` (float32 both): the norm of a sublayer's output on its way into the stream."""
         ops.rmsnorm_add(x, self.weight, self.eps, stream)
 
+    def add_to_then(self, x: torch.Tensor, stream: torch.Tensor, then: "Norm") -> torch.Tensor:
+        """``stream += norm(x)``, then ``then.forward(stream)``: one kernel when ``then`` is an RMS norm too."""
+        if type(then) is RMSNorm and then.weight.dtype == self.weight.dtype:
+            return ops.rmsnorm_add_norm(x, self.weight, self.eps, stream, then.weight, then.eps, self.ctx.dtype)
+        self.add_to(x, stream)
+        return then.forward(stream)
+
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.ctx.dtype, rows=rows)
 

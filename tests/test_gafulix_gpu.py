@@ -35,6 +35,34 @@ def test_norm_after_a_sublayer_adds_into_the_stream(ops):
     assert float((out.double().cpu() - ref).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [50, 256, 13000])
+def test_norm_after_a_sublayer_and_the_next_norm_in_one_kernel(ops, dtype, H):
+    x, w, s, w2 = rnd(5, H, seed=1, scale=3.0), (1 + 0.3 * rnd(H, seed=2)).to(dtype), rnd(5, H, seed=3), (1 + 0.3 * rnd(H, seed=4)).to(dtype)
+    stream = s.clone().to(DEV)
+    out = ops.rmsnorm_add_norm(x.to(DEV), w.to(DEV), 1e-3, stream, w2.to(DEV), 1e-5, dtype)
+    new = s.double() + plain.rms_norm(x.double(), w.double(), 1e-3)
+    assert float((stream.double().cpu() - new).abs().max()) < 1e-5
+    ref = plain.rms_norm(new, w2.double(), 1e-5)
+    assert out.dtype == dtype
+    assert float((out.double().cpu() - ref).abs().max()) <= (1e-5 if dtype == torch.float32 else 1e-2) * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("T,E,top", [(1, 5, 1), (8, 16, 2), (60, 3, 2), (3, 9, 9)])
+def test_choice_plan_and_regrouping_in_one_kernel_equal_the_three(ops, T, E, top):
+    H, tile = 40, 64
+    logits, x = rnd(T, E, seed=T, scale=2.0).to(DEV), rnd(T, H, seed=E).to(DEV)
+    wt, pos_of, tile_expert, xs = ops.moe_route_plan_scatter(logits, x, top, tile, scale_input=True)
+    sel, wt3 = ops.moe_route(logits, top)
+    pos3, te3 = ops.moe_plan(sel, E, tile)
+    xs3 = ops.moe_scatter(x, pos3, wt3, te3.numel() * tile, True)
+    assert torch.equal(wt, wt3) and torch.equal(tile_expert, te3)
+    # places within an expert's stretch may be dealt out in another order: compare by (token, choice)
+    assert torch.equal(pos_of // tile, pos3 // tile) or torch.equal(tile_expert[(pos_of // tile).long()], te3[(pos3 // tile).long()])
+    assert torch.equal(xs[pos_of.long()], xs3[pos3.long()])
+    assert len(set(pos_of.tolist())) == T * top
+
+
 @pytest.mark.parametrize("dims,base,scaling", [(16, 5000.0, tg.YARN_A), (64, 10000.0, tg.YARN_B), (32, 100.0, None),
                                                (96, 10000.0, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0})])
 def test_yarn_frequencies_and_magnitude(dims, base, scaling):
