@@ -480,6 +480,23 @@ def test_unequal_requests_together_and_slots_and_pages_used_again(name, dtype):
     assert eng.cache.slots.num_free == 2
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["wide", "mixed"])
+def test_a_long_request_in_portions_then_decoded(name, dtype):
+    """700 tokens: dozens of mask blocks and pages, a recurrent state that carries hundreds of tokens; prompt
+    portions that start and end inside blocks and pages, then 40 tokens one by one across a block edge."""
+    raw, page, tensors, _, _ = model(name, dtype)
+    ids = tg.prompt(700, raw["vocab"], 999)
+    ref = {"long": plain.plain_forward(raw, tensors, ids)}
+    eng = engine_for(name, dtype, num_pages=-(-700 // page) + 1, max_requests=1)
+    steps, at = [], 0
+    for n in (333, 2, 190, 135):
+        steps.append([("long", ids[at:at + n], at)])
+        at += n
+    steps += [[("long", [ids[i]], i)] for i in range(at, 700)]
+    check_rows(run_steps(eng, steps), ref, dtype, "long", routed(name))
+
+
 @pytest.mark.parametrize("name", list(tg.CONFIGS))
 def test_a_batch_changes_no_bit_of_a_request(name):
     """float32: a request's logits beside other requests equal its logits alone, bit for bit (every sum's
