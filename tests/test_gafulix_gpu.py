@@ -531,6 +531,34 @@ def test_greedy_generation_through_the_entry_point(name, tmp_path):
         assert list(g.token_ids) == ids[len(p):]
 
 
+def test_command_line_and_position_addressed_calls(tmp_path, capsys):
+    """`python -m blackwellllm_b200.cli -m DIR --prompt-ids ...` prints the plain implementation's greedy tokens; the
+    entry point's prefill() / forward() give the same tokens step by step."""
+    import os
+    from safetensors.torch import load_file
+    from blackwellllm_b200 import BlackwellEngine, InferenceConfig, cli
+    name = "looped"
+    raw, _ = tg.CONFIGS[name]
+    folder = tg.make_folder(name, "float32", str(tmp_path))
+    W = load_file(os.path.join(folder, "model.safetensors"))
+    prompt = tg.prompt(9, raw["vocab"], 4)
+    ids = list(prompt)
+    for _ in range(6):
+        ids.append(int(torch.argmax(plain.plain_forward(raw, W, ids)[-1])))
+    want = ids[len(prompt):]
+    rc = cli.main(["-m", folder, "--dtype", "float32", "--ctx", "128", "--temperature", "0", "--max-new-tokens", "6",
+                   "--prompt-ids", ",".join(map(str, prompt))])
+    out = capsys.readouterr().out
+    assert rc == 0 and [int(t) for t in out.strip().splitlines()[0].split()] == want
+    llm = BlackwellEngine(folder, InferenceConfig(max_context_length=128, max_batch_size=2), dtype="float32")
+    nxt = llm.prefill(prompt, start_pos=0, temperature=0.0, seq_id=0)
+    got = [nxt]
+    for i in range(5):
+        nxt = llm.forward(nxt, pos=len(prompt) + i, temperature=0.0, seq_id=0)
+        got.append(nxt)
+    assert got == want
+
+
 # =============================================================================== bin/trace_run
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
