@@ -64,10 +64,19 @@ class NoPositionSpec:
 
 
 @dataclass(frozen=True)
+class SinusoidalEmbeddingSpec:
+    """A vector of the token's position added to its embedding: entry 2i is sin(p * base^(-2i/width)), entry
+    2i + 1 the cosine of the same angle (positions count from 0 in each sequence)."""
+    base: float = 10000.0
+    kind: str = "sinusoidal"
+
+
+@dataclass(frozen=True)
 class RMSNormSpec:
     eps: float
     kind: str = "rmsnorm"
     param: str = "weight"   # the gain's name below the norm's prefix
+    offset: float = 0.0     # the gain is offset + the stored tensor (1: a weight that is stored around zero)
 
 
 @dataclass(frozen=True)
@@ -95,6 +104,19 @@ class AttentionSpec:
     v_head_dim: Optional[int] = None
     qk_norm_eps: Optional[float] = None
     names: Tuple[Tuple[str, str], ...] = ()
+    # ``qk_norm``: "whole" (above) or "head": every query head and every key head is normed by itself over its
+    # ``head_dim`` channels, with one gain vector of that size shared by the heads.  ``q_temperature`` =
+    # (coef, every): the queries of position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+    # ``sink``: a learned number per query head (tensor "sink") whose exponential joins the softmax's
+    # denominator; it has no key and no value and is not scaled.  ``output_gate``: the heads' outputs are
+    # multiplied element by element by sigmoid(W_g x) (tensor "g", [heads * value size, hidden]) before the
+    # output projection; x is the mixer's input.  ``shares_kv``: the mixer has no key and value tensors (no
+    # projections, no key norm) and reads the cache of another run of the schedule with its own queries.
+    qk_norm: str = "whole"
+    q_temperature: Optional[Tuple[float, float]] = None
+    sink: bool = False
+    output_gate: bool = False
+    shares_kv: bool = False
 
 
 @dataclass(frozen=True)
@@ -129,13 +151,54 @@ class RoutedFFNSpec:
     kind: str = "routed_ffn"
     router_name: str = "router"
     expert_names: Tuple[str, str, str, str] = ("e{e}.", "gate", "up", "down")
+    # ``identity_experts``: the router has this many outputs more than there are experts; the last ones stand
+    # for experts without tensors that return their input.  ``choice_bias``: the name of a vector with one entry
+    # per router output that is added to the scores for the CHOICE only (the weights stay the scores), or None.
+    # ``renorm_eps``: added to the sum that ``renormalize`` divides by.  ``activation``: the experts' gated
+    # activation, "silu" (silu(g) u) or "clamped_swish" (g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit),
+    # u' = clamp(u, -limit, limit)).  ``shared``: a dense gated feed-forward (a :class:`SwiGLUSpec`) that runs
+    # for every token and is added; its tensors lie below ``shared_prefix``.
+    identity_experts: int = 0
+    choice_bias: Optional[str] = None
+    renorm_eps: float = 0.0
+    activation: str = "silu"
+    act_limit: float = 0.0
+    act_alpha: float = 1.0
+    shared: Any = None
+    shared_prefix: str = "shared."
 
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """Dense gated feed-forward: down(silu(gate(x)) * up(x))."""
+    """Dense gated feed-forward: down(silu(gate(x)) * up(x)); with ``activation`` "clamped_swish":
+    down(g sigmoid(alpha g) (u + 1)), g = min(gate(x), limit), u = clamp(up(x), -limit, limit).
+    ``names``: the three tensors (gate, up, down) below the part's prefix."""
     intermediate_size: int
     kind: str = "swiglu"
+    activation: str = "silu"
+    act_limit: float = 0.0
+    act_alpha: float = 1.0
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """Dense feed-forward without a gate: down(act(up(x))); ``activation`` "relu2": max(z, 0)^2."""
+    intermediate_size: int
+    activation: str = "relu2"
+    kind: str = "dense_mlp"
+    names: Tuple[str, str] = ("up", "down")
+
+
+@dataclass(frozen=True)
+class HyperConnectionSpec:
+    """The stream as ``streams`` copies x_1 .. x_s.  Sublayer q of a layer reads u = sum_s in[s] x_s (through its
+    norm) and writes x_t <- sum_s mix[s, t] x_s + out[t] * y, all copies at once from the old ones.  The
+    tensors "in" [s], "out" [s], "mix" [s, s] lie below ``mixer_prefix`` / ``ffn_prefix`` of the layer."""
+    streams: int
+    mixer_prefix: str = "hc1."
+    ffn_prefix: str = "hc2."
+    optional_tensors: bool = False   # True: a missing tensor stands for in = out = 1, mix = identity (one copy only)
 
 
 @dataclass(frozen=True)
@@ -143,7 +206,8 @@ class LayerSpec:
     """One layer: which mixer, which feed-forward, which norms, arranged how.
 
     ``block`` names the arrangement (``"prenorm"``: x += mixer(norm(x));
-    x += ffn(norm(x)); ``"sandwich"``: the same with a second norm on each sublayer's output).  ``ffn`` may be ``None`` for a mixer-only layer.
+    x += ffn(norm(x)); ``"sandwich"``: the same with a second norm on each sublayer's output; ``"hyper"``:
+    pre-norm sublayers over several copies of the stream, see ``hyper``).  ``ffn`` may be ``None`` for a mixer-only layer.
     """
     mixer: Any
     ffn: Any
@@ -161,6 +225,8 @@ class LayerSpec:
     ffn_post_norm: Any = None
     mixer_post_norm_prefix: str = ""
     ffn_post_norm_prefix: str = ""
+    # the "hyper" arrangement keeps several copies of the stream (a :class:`HyperConnectionSpec`)
+    hyper: Any = None
 
 
 @dataclass(frozen=True)
@@ -197,6 +263,10 @@ class ModelConfig:
     embedding_multiplier: float = 1.0
     logit_scale: float = 1.0
     logit_softcap: Optional[float] = None
+    # a vector of the position added to the embedding's output (a :class:`SinusoidalEmbeddingSpec`), and the
+    # number of copies the stream is kept in (None: one plain stream; a number: every layer is a "hyper" block)
+    position_embedding: Any = None
+    streams: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
     stored_dtype: str = "bfloat16"

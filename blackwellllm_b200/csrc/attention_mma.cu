@@ -43,6 +43,9 @@ struct Params {
     float* part_o; float* part_ml; // slices' partial results (attn_keys_kernel)
     int max_blocks, nh, nkv, G, page_size, num_pages, window, chunk;
     float scale_log2;
+    // sink != null: a row's softmax has one more term exp(sink[query head]) that has no key and no value
+    // (its weight goes nowhere: the row's weights sum to less than one); float32 [nh], not scaled.
+    const float* sink;
     // Decode rows straight from the q/k/v product (attn_keys_tma_kernel only; null: q holds the queries and
     // the cache this step's keys and values): qkv is float32 [planes][tokens][(nh + 2 nkv) * HD] to be added
     // up in plane order, the rotated channels of the q and k heads as (channel j, channel j + rd / 2) pairs;
@@ -51,6 +54,11 @@ struct Params {
     const float* qkv; long long qkv_plane_stride; const float* rope_table;
     int qkv_planes, rd, append;
 };
+
+// The sink's term of a row's denominator, in the units of the running sums (powers of two, maximum M taken off).
+__device__ __forceinline__ float sink_term(const Params& p, int head, float M) {
+    return p.sink ? exp2f(p.sink[head] * 1.4426950408889634f - M) : 0.f;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -311,8 +319,9 @@ attn_rows_kernel(Params p, int toks_per_tile) {
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int row = warp * 16 + (lane >> 2) + 8 * h;
         if (row >= n_rows) continue;
-        const float inv = l > 0.f ? 1.f / l : 0.f;
         const int tok = row / p.G, hg = row - tok * p.G;
+        l += sink_term(p, g * p.G + hg, st.m[h]);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
         bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok0 + tok) * p.nh + g * p.G + hg) * HD + 2 * (lane & 3);
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j)
@@ -360,6 +369,7 @@ __device__ __forceinline__ void finish_keys(const Params& p, const RowState& st,
         }
         const int tok = row / p.G, hg = row - tok * p.G;
         if (n_slices == 1) {
+            L += sink_term(p, g * p.G + hg, M);
             p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] =
                 __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
         } else {
@@ -811,8 +821,9 @@ attn_merge_kernel(Params p, const int* merge_items) {
         }
         float L = 0.f;
         for (int sl = 0; sl < n_slices; ++sl) L += sm_lf[sl];
-        const float inv = L > 0.f ? 1.f / L : 0.f;
         const int tok = row / p.G, hg = row - tok * p.G;
+        L += sink_term(p, g * p.G + hg, M);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
         bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + tid * 4;
         const uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         *reinterpret_cast<uint2*>(dst) = packed;
@@ -856,8 +867,9 @@ attn_merge_few_kernel(Params p, const int* merge_items) {
         acc.x += part[sl].x * f; acc.y += part[sl].y * f; acc.z += part[sl].z * f; acc.w += part[sl].w * f;
         L += ml[sl].y * f;
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
     const int tok = row / p.G, hg = row - tok * p.G;
+    L += sink_term(p, g * p.G + hg, M);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
     bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + quad * 4;
     *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
 }
@@ -880,6 +892,7 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 // the q/k/v product itself: float32 [qkv_planes][tokens][(nh + 2 nkv) * HD], the planes qkv_plane_stride
 // floats apart and added in order, the rotated channels of the q and k heads as (j, j + rd / 2) pairs;
 // rope_table float32 [tokens][rd] (cosines, then sines); append != 0: key and value also go to the cache.
+// sink: float32 [nh] or null (see Params).
 // Only where the TMA key-slice kernel runs (head size a multiple of 64, pages of 8 to 64 tokens);
 // BW_ERR_UNSUPPORTED otherwise, and nothing was launched.
 BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
@@ -888,7 +901,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
                                const int* merge_work, int n_merge_items, float* part_o, float* part_ml, int nh,
                                int nkv, int page_size, int num_pages, int window, int chunk, float scale,
                                const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
-                               int rd, int append, int merge_max_slices, void* stream) {
+                               int rd, int append, int merge_max_slices, const float* sink, void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
@@ -911,6 +924,7 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.sink = sink;
     p.qkv = qkv; p.qkv_plane_stride = qkv_plane_stride; p.rope_table = rope_table;
     p.qkv_planes = qkv_planes; p.rd = rd; p.append = append;
     if (n_rows_items > 0) {

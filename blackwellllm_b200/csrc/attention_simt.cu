@@ -22,7 +22,7 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                       const KT* __restrict__ v_pages, const int* __restrict__ positions,
                       const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                       int max_blocks, OT* __restrict__ out, int nh, int nkv, int hd, int page_size,
-                      int num_pages, int window, int chunk, float scale) {
+                      int num_pages, int window, int chunk, float scale, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     float* qs = smem;                       // [hd]
     float* accs = qs + hd;                  // [WARPS][hd]
@@ -97,6 +97,7 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
         f[w] = (ml[w * 2] == -INFINITY) ? 0.f : expf(ml[w * 2] - M);
         L += ml[w * 2 + 1] * f[w];
     }
+    if (sink) L += expf(sink[h] - M);   // one more term of the softmax, without a key or a value
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int c = threadIdx.x; c < hd; c += blockDim.x) {
         float o = 0.f;
@@ -107,11 +108,12 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
 
 }  // namespace
 
+// sink: float32 [nh] or null: exp(sink[head]) joins every row's softmax denominator (unscaled, no key, no value).
 // type: element type of q, the pages and out (all the same).  window <= 0: no window; chunk <= 0: no blocks (bw::first_visible).
 BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* v_pages, int type,
                                 const int* positions, const int* req_of_token, const int* block_table,
                                 int max_blocks, void* out, int T, int nh, int nkv, int hd, int page_size,
-                                int num_pages, int window, int chunk, float scale, void* stream) {
+                                int num_pages, int window, int chunk, float scale, const float* sink, void* stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 32 * MAX_CH || nkv <= 0 || nh % nkv != 0) return BW_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -120,11 +122,11 @@ BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* 
     if (type == BW_F32)
         attention_simt_kernel<float, float, float><<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_pages, (const float*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale);
+            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink);
     else if (type == BW_BF16)
         attention_simt_kernel<bf16, bf16, bf16><<<grid, WARPS * 32, smem, s>>>(
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale);
+            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;

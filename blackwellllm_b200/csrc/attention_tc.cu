@@ -56,6 +56,7 @@ struct Params {
     const int* cu_q; const int* q_start; const int* kv_len; const int* block_table; const int* work;
     int max_blocks, nh, nkv, G, page_size, window, chunk, tpt;
     float scale_log2;
+    const float* sink;   // float32 [nh] or null: exp(sink[query head]) joins the row's softmax denominator (no key, no value, not scaled)
 };
 
 // 2^x, one MUFU instruction (the flush of denormal results to zero does not matter for softmax weights)
@@ -314,6 +315,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         if (ok) ok = __all_sync(0xffffffffu, bw::mbar_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, &g_status, 18));
         if (ok) {
             bw::tc_fence_after();
+            if (p.sink) l += exp2f(p.sink[g * p.G + hg] * 1.4426950408889634f - m);   // m: the maximum that l is counted from
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok0 + tok) * p.nh + g * p.G + hg) * HD;
 #pragma unroll
@@ -383,7 +385,7 @@ BW_EXPORT int bw_attention_tc_supported(int nh, int nkv, int page_size) {
 BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                               const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                               const int* work, int n_items, int T, int nh, int nkv, int page_size, int num_pages,
-                              int window, int chunk, float scale, void* stream) {
+                              int window, int chunk, float scale, const float* sink, void* stream) {
     if (n_items <= 0) return 0;
     if (!bw_attention_tc_supported(nh, nkv, page_size) || !(scale > 0.f)) return BW_ERR_UNSUPPORTED;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return BW_ERR_UNSUPPORTED;
@@ -408,6 +410,7 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     p.work = work; p.max_blocks = max_blocks; p.nh = nh; p.nkv = nkv; p.G = G; p.page_size = page_size;
     p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0; p.tpt = tpt;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.sink = sink;
     bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();
     return 0;

@@ -19,6 +19,14 @@
 #define BW_F32  0
 #define BW_BF16 1
 
+// activations of feed-forwards (the codes cross the C interface)
+//   BW_ACT_SILU           gated:  silu(g) * u
+//   BW_ACT_CLAMPED_SWISH  gated:  g' = min(g, limit), u' = clamp(u, -limit, limit):  g' sigmoid(alpha g') (u' + 1)
+//   BW_ACT_RELU2          no gate: max(x, 0)^2
+#define BW_ACT_SILU 0
+#define BW_ACT_CLAMPED_SWISH 1
+#define BW_ACT_RELU2 2
+
 // Programmatic dependent launch: a kernel launched through bw::launch may start while the kernel
 // before it in the stream is still draining.  Such a kernel calls BW_PDL_TRIGGER() early (the next
 // kernel may start launching) and BW_PDL_WAIT() before its first access to memory that an earlier
@@ -122,6 +130,19 @@ __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162flo
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float glu(int act, float g, float u, float limit, float alpha) {
+    if (act == BW_ACT_CLAMPED_SWISH) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+    }
+    return g / (1.f + expf(-g)) * u;
+}
+__device__ __forceinline__ float unary_act(int act, float x) {
+    if (act == BW_ACT_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+    return x;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

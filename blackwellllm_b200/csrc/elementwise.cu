@@ -27,6 +27,32 @@ __global__ void embed_gather_kernel(const WT* __restrict__ table, const int* __r
     }
 }
 
+// The same with a sine/cosine vector of the token's position added, written `copies` times side by side
+// (out [T, copies, H]): entry 2i is sin(pos * inv_freq[i]), entry 2i + 1 the cosine of the same angle.  The
+// angle is the float32 product of the position and the frequency; sine and cosine are the precise ones.
+// inv_freq == null: no position vector.
+template <typename WT>
+__global__ void embed_positions_kernel(const WT* __restrict__ table, const int* __restrict__ ids,
+                                       const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                       float* __restrict__ out, int H, int V, float scale, int copies) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) id = 0;  // the host rejects such ids before the launch
+    const WT* row = table + (size_t)id * H;
+    float* o = out + (size_t)t * copies * H;
+    const float pos = (float)positions[t];
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = bw::to_f32(row[c]) * scale;
+        if (inv_freq) {
+            const float ang = pos * inv_freq[c >> 1];
+            v += (c & 1) ? cosf(ang) : sinf(ang);
+        }
+        for (int k = 0; k < copies; ++k) o[(size_t)k * H + c] = v;
+    }
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // y = x * rsqrt(mean(x^2) + eps) * w.  One block per output row; input row is
 // rows[i] when `rows` is given (final norm on the rows whose logits are wanted).
@@ -168,10 +194,12 @@ __global__ void add_planes_kernel(float* __restrict__ x, const float* __restrict
     }
 }
 
-// ---------------------------------------------------------------- SwiGLU
-// in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I].
+// ---------------------------------------------------------------- SwiGLU and other activations
+// in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I] = bw::glu(act, gate, up, limit, alpha)
+// (BW_ACT_SILU: silu(gate) * up).
 template <typename IT, typename OT>
-__global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, int I, size_t total, int act, float limit,
+                              float alpha) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -179,8 +207,32 @@ __global__ void swiglu_kernel(const IT* __restrict__ gu, OT* __restrict__ out, i
         const size_t t = idx / I; const int c = (int)(idx - t * I);
         const float g = bw::to_f32(gu[t * 2 * (size_t)I + c]);
         const float u = bw::to_f32(gu[t * 2 * (size_t)I + I + c]);
-        const float s = g / (1.f + expf(-g));
-        out[idx] = bw::from_f32<OT>(s * u);
+        out[idx] = bw::from_f32<OT>(bw::glu(act, g, u, limit, alpha));
+    }
+}
+
+// An activation without a gate, element by element: BW_ACT_RELU2: max(x, 0)^2.
+template <typename IT, typename OT>
+__global__ void unary_act_kernel(const IT* __restrict__ x, OT* __restrict__ out, size_t total, int act) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = bw::from_f32<OT>(bw::unary_act(act, bw::to_f32(x[idx])));
+}
+
+// o[t, h, c] *= sigmoid(g[t, h * dv + c]) for c < dv (o has dpad >= dv channels a head; those beyond dv become 0):
+// the output gate of a mixer.  g: float32 rows `ld` apart.  One block per token.
+template <typename OT>
+__global__ void sigmoid_gate_kernel(OT* __restrict__ o, const float* __restrict__ g, long long ld, int nh, int dv, int dpad) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    OT* orow = o + (size_t)blockIdx.x * nh * dpad;
+    const float* grow = g + (size_t)blockIdx.x * ld;
+    for (int idx = threadIdx.x; idx < nh * dpad; idx += blockDim.x) {
+        const int h = idx / dpad, c = idx - h * dpad;
+        float v = 0.f;
+        if (c < dv) v = bw::to_f32(orow[idx]) / (1.f + expf(-grow[(size_t)h * dv + c]));
+        orow[idx] = bw::from_f32<OT>(v);
     }
 }
 
@@ -401,6 +453,20 @@ BW_EXPORT int bw_embed_gather(const void* table, int table_type, const int* ids,
     return 0;
 }
 
+// out float32 [T, copies, H]; inv_freq float32 [ceil(H / 2)] or null (no position vector)
+BW_EXPORT int bw_embed_positions(const void* table, int table_type, const int* ids, const int* positions,
+                                 const float* inv_freq, float* out, int T, int H, int V, float scale, int copies, void* stream) {
+    if (T <= 0) return 0;
+    if (copies <= 0 || H <= 0) return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_type == BW_F32) bw::launch((embed_positions_kernel<float>), dim3(T), dim3(threads), 0, s, cp<float>(table), ids, positions, inv_freq, out, H, V, scale, copies);
+    else if (table_type == BW_BF16) bw::launch((embed_positions_kernel<bf16>), dim3(T), dim3(threads), 0, s, cp<bf16>(table), ids, positions, inv_freq, out, H, V, scale, copies);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
 BW_EXPORT int bw_rmsnorm(const float* x, const void* w, int w_type, const int* rows, void* out,
                          int out_type, int n_rows, int H, float eps, void* stream) {
     if (n_rows <= 0) return 0;
@@ -493,15 +559,55 @@ BW_EXPORT int bw_add_planes(float* x, const float* planes, int n_planes, long lo
     return 0;
 }
 
+static int launch_glu(const void* gu, int in_type, void* out, int out_type, int T, int I, int act, float limit, float alpha, void* stream);
+
 BW_EXPORT int bw_swiglu(const void* gu, int in_type, void* out, int out_type, int T, int I, void* stream) {
+    return launch_glu(gu, in_type, out, out_type, T, I, BW_ACT_SILU, 0.f, 1.f, stream);
+}
+
+// act: a gated activation of common.cuh (BW_ACT_SILU, BW_ACT_CLAMPED_SWISH with its limit and alpha)
+BW_EXPORT int bw_glu(const void* gu, int in_type, void* out, int out_type, int T, int I, int act, float limit, float alpha,
+                     void* stream) {
+    if (act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH) return BW_ERR_BAD_ARG;
+    return launch_glu(gu, in_type, out, out_type, T, I, act, limit, alpha, stream);
+}
+
+// out[i] = act(x[i]) over n elements; act: BW_ACT_RELU2
+BW_EXPORT int bw_unary_act(const void* x, int in_type, void* out, int out_type, long long n, int act, void* stream) {
+    if (n <= 0) return 0;
+    if (act != BW_ACT_RELU2) return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
+    if (in_type == BW_F32 && out_type == BW_F32) bw::launch((unary_act_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, cp<float>(x), mp<float>(out), (size_t)n, act);
+    else if (in_type == BW_BF16 && out_type == BW_BF16) bw::launch((unary_act_kernel<bf16, bf16>), dim3(blocks), dim3(threads), 0, s, cp<bf16>(x), mp<bf16>(out), (size_t)n, act);
+    else if (in_type == BW_F32 && out_type == BW_BF16) bw::launch((unary_act_kernel<float, bf16>), dim3(blocks), dim3(threads), 0, s, cp<float>(x), mp<bf16>(out), (size_t)n, act);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+// o [T, nh, dpad] of o_type, in place; g float32 [T, >= nh * dv] with rows ld floats apart
+BW_EXPORT int bw_sigmoid_gate(void* o, int o_type, const float* g, long long ld, int T, int nh, int dv, int dpad, void* stream) {
+    if (T <= 0) return 0;
+    if (nh <= 0 || dv <= 0 || dpad < dv || ld < (long long)nh * dv) return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (o_type == BW_F32) bw::launch((sigmoid_gate_kernel<float>), dim3(T), dim3(256), 0, s, mp<float>(o), g, ld, nh, dv, dpad);
+    else if (o_type == BW_BF16) bw::launch((sigmoid_gate_kernel<bf16>), dim3(T), dim3(256), 0, s, mp<bf16>(o), g, ld, nh, dv, dpad);
+    else return BW_ERR_BAD_ARG;
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+static int launch_glu(const void* gu, int in_type, void* out, int out_type, int T, int I, int act, float limit, float alpha, void* stream) {
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)T * I;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (in_type == BW_F32 && out_type == BW_F32) bw::launch((swiglu_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, cp<float>(gu), mp<float>(out), I, total);
-    else if (in_type == BW_BF16 && out_type == BW_BF16) bw::launch((swiglu_kernel<bf16, bf16>), dim3(blocks), dim3(threads), 0, s, cp<bf16>(gu), mp<bf16>(out), I, total);
-    else if (in_type == BW_F32 && out_type == BW_BF16) bw::launch((swiglu_kernel<float, bf16>), dim3(blocks), dim3(threads), 0, s, cp<float>(gu), mp<bf16>(out), I, total);
+    if (in_type == BW_F32 && out_type == BW_F32) bw::launch((swiglu_kernel<float, float>), dim3(blocks), dim3(threads), 0, s, cp<float>(gu), mp<float>(out), I, total, act, limit, alpha);
+    else if (in_type == BW_BF16 && out_type == BW_BF16) bw::launch((swiglu_kernel<bf16, bf16>), dim3(blocks), dim3(threads), 0, s, cp<bf16>(gu), mp<bf16>(out), I, total, act, limit, alpha);
+    else if (in_type == BW_F32 && out_type == BW_BF16) bw::launch((swiglu_kernel<float, bf16>), dim3(blocks), dim3(threads), 0, s, cp<float>(gu), mp<bf16>(out), I, total, act, limit, alpha);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;

@@ -5,7 +5,11 @@
 // (a decode step stays capturable in a CUDA graph).
 //
 //   moe_route    one warp per token: score = sigmoid(logit) (or softmax), the `top` largest scores
-//                (lowest index on ties), optionally renormalised to sum 1; float32 throughout
+//                (lowest index on ties), optionally renormalised to sum 1; float32 throughout.  With a bias
+//                per router output the CHOICE goes by score + bias while the weights stay the scores.
+//                The router may have more outputs than there are experts: outputs from `E` (the experts
+//                that have weights) up to `E_total` stand for experts that return their input; their rows
+//                take no part in the regrouping and the products, and moe_combine adds weight * x for them
 //   moe_plan     one block: rows per expert, each expert's stretch padded to whole tiles (64 rows here, 128 in moe_tc.cu),
 //                the place of every (token, choice) row, and the expert of every tile
 //   moe_scatter  the regrouped operand: row (token, choice) = weight * x[token] (input scaling) or x[token]
@@ -50,8 +54,11 @@ __device__ __forceinline__ void scale_row(const bf16* __restrict__ src, bf16* __
 }
 
 // ---------------------------------------------------------------- routing
+// E: the router's outputs; bias: float32 [E] added to the scores for the choice only, or null; renorm_eps: added to
+// the sum of the chosen scores before they are divided by it
 __device__ __forceinline__ void route_token(const float* __restrict__ logits, int t, int lane, int E, int top, int softmax,
-                                            int renorm, int* __restrict__ sel, float* __restrict__ wt) {
+                                            int renorm, const float* __restrict__ bias, float renorm_eps,
+                                            int* __restrict__ sel, float* __restrict__ wt) {
     const float* z = logits + (size_t)t * E;
     float zmax = -INFINITY, zsum = 0.f;
     if (softmax) {
@@ -61,39 +68,43 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, in
         zsum = bw::warp_sum(zsum);
     }
     float total = 0.f;
-    int last = -1; float last_s = INFINITY;   // choices are taken in order of (score descending, index ascending)
+    int last = -1; float last_s = INFINITY;   // choices are taken in order of (choice score descending, index ascending)
     for (int k = 0; k < top; ++k) {
-        float best = -INFINITY; int bi = 0x7fffffff;
+        float best = -INFINITY, best_w = 0.f; int bi = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float s = softmax ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
+            const float w = softmax ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
+            const float s = bias ? w + bias[e] : w;
             const bool after = (s < last_s) || (s == last_s && e > last);   // not chosen yet
-            if (after && (s > best || (s == best && e < bi))) { best = s; bi = e; }
+            if (after && (s > best || (s == best && e < bi))) { best = s; best_w = w; bi = e; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const float ow = __shfl_xor_sync(0xffffffffu, best_w, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+            if (ob > best || (ob == best && oi < bi)) { best = ob; best_w = ow; bi = oi; }
         }
-        last = bi; last_s = best; total += best;
-        if (lane == 0) { sel[(size_t)t * top + k] = bi; wt[(size_t)t * top + k] = best; }
+        last = bi; last_s = best; total += best_w;
+        if (lane == 0) { sel[(size_t)t * top + k] = bi; wt[(size_t)t * top + k] = best_w; }
     }
+    total += renorm_eps;
     if (renorm && lane == 0 && total > 0.f)
         for (int k = 0; k < top; ++k) wt[(size_t)t * top + k] /= total;
 }
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int softmax, int renorm,
-                 int* __restrict__ sel, float* __restrict__ wt) {
+                 const float* __restrict__ bias, float renorm_eps, int* __restrict__ sel, float* __restrict__ wt) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
-    route_token(logits, t, lane, E, top, softmax, renorm, sel, wt);
+    route_token(logits, t, lane, E, top, softmax, renorm, bias, renorm_eps, sel, wt);
 }
 
 // ---------------------------------------------------------------- plan
-// pos_of[n] for the n = T * top rows (token-major); tile_expert[max_tiles] (-1: idle tile).
+// pos_of[n] for the n = T * top rows (token-major; -1 for a row whose choice is no expert with weights, i.e. >= E);
+// tile_expert[max_tiles] (-1: idle tile).
 __device__ __forceinline__ void plan_block(const int* __restrict__ sel, int n, int E, int tile_rows, int max_tiles,
                                            int* __restrict__ pos_of, int* __restrict__ tile_expert, int* sh) {
     int* count = sh;          // [E]
@@ -102,7 +113,7 @@ __device__ __forceinline__ void plan_block(const int* __restrict__ sel, int n, i
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int e = sel[i];
-        pos_of[i] = (e >= 0 && e < E) ? atomicAdd(&count[e], 1) : 0;
+        pos_of[i] = (e >= 0 && e < E) ? atomicAdd(&count[e], 1) : -1;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -141,7 +152,8 @@ moe_plan_kernel(const int* __restrict__ sel, int n, int E, int tile_rows, int ma
 // without two more launches.  The block's own writes to sel, wt and pos_of are read back after a barrier.
 template <typename XT>
 __global__ void __launch_bounds__(1024)
-moe_route_plan_scatter_kernel(const float* __restrict__ logits, int T, int E, int top, int softmax, int renorm,
+moe_route_plan_scatter_kernel(const float* __restrict__ logits, int T, int E, int E_total, int top, int softmax, int renorm,
+                              const float* __restrict__ bias, float renorm_eps,
                               int* __restrict__ sel, float* __restrict__ wt, int tile_rows, int max_tiles,
                               int* __restrict__ pos_of, int* __restrict__ tile_expert, const XT* __restrict__ x,
                               XT* __restrict__ xs, int H, int scale_input) {
@@ -149,11 +161,12 @@ moe_route_plan_scatter_kernel(const float* __restrict__ logits, int T, int E, in
     BW_PDL_WAIT();
     extern __shared__ int sh[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int t = warp; t < T; t += 32) route_token(logits, t, lane, E, top, softmax, renorm, sel, wt);
+    for (int t = warp; t < T; t += 32) route_token(logits, t, lane, E_total, top, softmax, renorm, bias, renorm_eps, sel, wt);
     __syncthreads();
     plan_block(sel, T * top, E, tile_rows, max_tiles, pos_of, tile_expert, sh);
     __syncthreads();
     for (int i = warp; i < T * top; i += 32) {
+        if (pos_of[i] < 0) continue;
         const float w = scale_input ? wt[i] : 1.f;
         const XT* src = x + (size_t)(i / top) * H;
         XT* dst = xs + (size_t)pos_of[i] * H;
@@ -169,6 +182,7 @@ moe_scatter_kernel(const XT* __restrict__ x, const int* __restrict__ pos_of, con
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     const int i = blockIdx.x;                 // (token, choice)
+    if (pos_of[i] < 0) return;                // an expert without weights: nothing to regroup
     const int t = i / top;
     const float w = scale_input ? wt[i] : 1.f;
     const XT* src = x + (size_t)t * H;
@@ -181,7 +195,7 @@ moe_scatter_kernel(const XT* __restrict__ x, const int* __restrict__ pos_of, con
 template <typename AT, typename CT, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const AT* __restrict__ A, const AT* __restrict__ W, const AT* __restrict__ W2,
-                const int* __restrict__ tile_expert, CT* __restrict__ C, int N, int K) {
+                const int* __restrict__ tile_expert, CT* __restrict__ C, int N, int K, int act, float limit, float alpha) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     const int e = tile_expert[blockIdx.x];
@@ -228,17 +242,29 @@ moe_gemm_kernel(const AT* __restrict__ A, const AT* __restrict__ W, const AT* __
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             float v = acc[i][j];
-            if constexpr (GATED) v = v / (1.f + expf(-v)) * acc2[i][j];
+            if constexpr (GATED) v = bw::glu(act, v, acc2[i][j], limit, alpha);
             C[(size_t)(row0 + ty * 4 + i) * N + n] = bw::from_f32<CT>(v);
         }
 }
 
 // ---------------------------------------------------------------- combine
-// mode 0: out = sum; 1: out += sum; 2: out += sum / rms(sum) * gain.  One block per token.
+// mode 0: out = sum; 1: out += sum; 2: out += sum / rms(sum) * gain.  One block per token.  A choice without a
+// place (pos_of < 0: an expert that returns its input) contributes the token's own row of x.
+template <typename XT>
+__device__ __forceinline__ float4 row4(const XT* p);
+template <> __device__ __forceinline__ float4 row4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 row4<bf16>(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename XT>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, const float* __restrict__ wt,
                    int top, int scale_output, float* __restrict__ out, int H, int mode,
-                   const float* __restrict__ gain, float eps) {
+                   const float* __restrict__ gain, float eps, const XT* __restrict__ x) {
     BW_PDL_TRIGGER();
     BW_PDL_WAIT();
     extern __shared__ __align__(16) float row[];    // [H]
@@ -251,7 +277,9 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, 
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int k = 0; k < top; ++k) {
                 const float w = scale_output ? wt[(size_t)t * top + k] : 1.f;
-                const float4 a = *reinterpret_cast<const float4*>(y + (size_t)pos_of[(size_t)t * top + k] * H + c);
+                const int at = pos_of[(size_t)t * top + k];
+                const float4 a = at >= 0 ? *reinterpret_cast<const float4*>(y + (size_t)at * H + c)
+                                         : (x ? row4<XT>(x + (size_t)t * H + c) : make_float4(0.f, 0.f, 0.f, 0.f));
                 v.x = fmaf(w, a.x, v.x); v.y = fmaf(w, a.y, v.y); v.z = fmaf(w, a.z, v.z); v.w = fmaf(w, a.w, v.w);
             }
             *reinterpret_cast<float4*>(row + c) = v;
@@ -262,7 +290,8 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, 
             float v = 0.f;
             for (int k = 0; k < top; ++k) {
                 const float w = scale_output ? wt[(size_t)t * top + k] : 1.f;
-                v = fmaf(w, y[(size_t)pos_of[(size_t)t * top + k] * H + c], v);
+                const int at = pos_of[(size_t)t * top + k];
+                v = fmaf(w, at >= 0 ? y[(size_t)at * H + c] : (x ? bw::to_f32(x[(size_t)t * H + c]) : 0.f), v);
             }
             row[c] = v;
             ss = fmaf(v, v, ss);
@@ -295,11 +324,13 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of, 
 
 BW_EXPORT int bw_moe_tile_rows() { return TILE_M; }
 
-BW_EXPORT int bw_moe_route(const float* logits, int T, int E, int top, int softmax, int renorm, int* sel, float* wt,
-                           void* stream) {
+// E: the router's outputs (logits [T, E]); bias: float32 [E] or null; renorm_eps: see route_token
+BW_EXPORT int bw_moe_route(const float* logits, int T, int E, int top, int softmax, int renorm, const float* bias,
+                           float renorm_eps, int* sel, float* wt, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E) return BW_ERR_BAD_ARG;
-    bw::launch((moe_route_kernel), dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, T, E, top, softmax, renorm, sel, wt);
+    bw::launch((moe_route_kernel), dim3((T + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits, T, E, top, softmax, renorm, bias,
+               renorm_eps, sel, wt);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -325,16 +356,19 @@ BW_EXPORT int bw_moe_scatter(const void* x, int type, const int* pos_of, const f
     return 0;
 }
 
-BW_EXPORT int bw_moe_route_plan_scatter(const float* logits, int T, int E, int top, int softmax, int renorm, int* sel, float* wt,
+// E: experts with weights; E_total >= E: the router's outputs (logits [T, E_total], bias [E_total] or null)
+BW_EXPORT int bw_moe_route_plan_scatter(const float* logits, int T, int E, int E_total, int top, int softmax, int renorm,
+                                        const float* bias, float renorm_eps, int* sel, float* wt,
                                         int tile_rows, int max_tiles, int* pos_of, int* tile_expert, const void* x, int type,
                                         void* xs, int H, int scale_input, void* stream) {
     if (T <= 0) return 0;
     const int n = T * top;
-    if (E <= 0 || E > 4096 || top <= 0 || top > E || n > 1024 || tile_rows <= 0 || max_tiles < (n + tile_rows - 1) / tile_rows + E)
+    if (E <= 0 || E > 4096 || E_total < E || top <= 0 || top > E_total || n > 1024 || tile_rows <= 0 ||
+        max_tiles < (n + tile_rows - 1) / tile_rows + E)
         return BW_ERR_BAD_ARG;
     const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
     cudaStream_t s = (cudaStream_t)stream;
-#define BW_RPS(XT) bw::launch((moe_route_plan_scatter_kernel<XT>), dim3(1), dim3(1024), smem, s, logits, T, E, top, softmax, renorm, sel, wt, \
+#define BW_RPS(XT) bw::launch((moe_route_plan_scatter_kernel<XT>), dim3(1), dim3(1024), smem, s, logits, T, E, E_total, top, softmax, renorm, bias, renorm_eps, sel, wt, \
         tile_rows, max_tiles, pos_of, tile_expert, (const XT*)x, (XT*)xs, H, scale_input)
     if (type == BW_F32) BW_RPS(float);
     else if (type == BW_BF16) BW_RPS(bf16);
@@ -344,14 +378,15 @@ BW_EXPORT int bw_moe_route_plan_scatter(const float* logits, int T, int E, int t
     return 0;
 }
 
-// type: element type of A and the weights; c_type: of C.  w2 non-null: C = silu(A w^T) * (A w2^T).
+// type: element type of A and the weights; c_type: of C.  w2 non-null: C = glu(A w^T, A w2^T) with the gated
+// activation `act` of common.cuh (BW_ACT_SILU: silu(A w^T) * (A w2^T)) and its limit and alpha.
 BW_EXPORT int bw_moe_gemm(const void* A, const void* w, const void* w2, int type, const int* tile_expert, void* C, int c_type,
-                          int max_tiles, int N, int K, void* stream) {
+                          int max_tiles, int N, int K, int act, float limit, float alpha, void* stream) {
     if (max_tiles <= 0) return 0;
     if (N <= 0 || K <= 0) return BW_ERR_BAD_ARG;
     const dim3 grid(max_tiles, (N + BN - 1) / BN);
     cudaStream_t s = (cudaStream_t)stream;
-#define BW_MG(AT, CT, G) bw::launch((moe_gemm_kernel<AT, CT, G>), grid, dim3(256), 0, s, (const AT*)A, (const AT*)w, (const AT*)w2, tile_expert, (CT*)C, N, K)
+#define BW_MG(AT, CT, G) bw::launch((moe_gemm_kernel<AT, CT, G>), grid, dim3(256), 0, s, (const AT*)A, (const AT*)w, (const AT*)w2, tile_expert, (CT*)C, N, K, act, limit, alpha)
     if (type == BW_F32 && c_type == BW_F32) { if (w2) BW_MG(float, float, true); else BW_MG(float, float, false); }
     else if (type == BW_BF16 && c_type == BW_BF16) { if (w2) BW_MG(bf16, bf16, true); else BW_MG(bf16, bf16, false); }
     else if (type == BW_BF16 && c_type == BW_F32) { if (w2) BW_MG(bf16, float, true); else BW_MG(bf16, float, false); }
@@ -361,14 +396,23 @@ BW_EXPORT int bw_moe_gemm(const void* A, const void* w, const void* w2, int type
     return 0;
 }
 
+// x (of x_type, [T, H]): the experts' input, read for choices without a place (experts that return their input);
+// null where there are none.
 BW_EXPORT int bw_moe_combine(const float* y, const int* pos_of, const float* wt, int top, int scale_output, float* out, int T,
-                             int H, int mode, const float* gain, float eps, void* stream) {
+                             int H, int mode, const float* gain, float eps, const void* x, int x_type, void* stream) {
     if (T <= 0) return 0;
     if (mode < 0 || mode > 2 || (mode == 2 && !gain) || (size_t)H * sizeof(float) > 200 * 1024) return BW_ERR_BAD_ARG;
-    static bool raised[bw::MAX_DEVICES] = {};
+    static bool raised[bw::MAX_DEVICES] = {}, raised_bf16[bw::MAX_DEVICES] = {};
     const size_t smem = (size_t)H * sizeof(float);
-    if (smem > 48 * 1024 && bw::allow_dynamic_smem(moe_combine_kernel, 200 * 1024, raised) != cudaSuccess) return BW_ERR_DRIVER;
-    bw::launch((moe_combine_kernel), dim3(T), dim3(256), smem, (cudaStream_t)stream, y, pos_of, wt, top, scale_output, out, H, mode, gain, eps);
+    if (x && x_type == BW_BF16) {
+        if (smem > 48 * 1024 && bw::allow_dynamic_smem(moe_combine_kernel<bf16>, 200 * 1024, raised_bf16) != cudaSuccess) return BW_ERR_DRIVER;
+        bw::launch((moe_combine_kernel<bf16>), dim3(T), dim3(256), smem, (cudaStream_t)stream, y, pos_of, wt, top, scale_output, out, H,
+                   mode, gain, eps, (const bf16*)x);
+    } else if (!x || x_type == BW_F32) {
+        if (smem > 48 * 1024 && bw::allow_dynamic_smem(moe_combine_kernel<float>, 200 * 1024, raised) != cudaSuccess) return BW_ERR_DRIVER;
+        bw::launch((moe_combine_kernel<float>), dim3(T), dim3(256), smem, (cudaStream_t)stream, y, pos_of, wt, top, scale_output, out, H,
+                   mode, gain, eps, (const float*)x);
+    } else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;
 }

@@ -28,7 +28,7 @@ __device__ int g_status = 0;
 template <bool GATED, typename CT>
 __global__ void __launch_bounds__(THREADS)
 moe_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-              const int* __restrict__ tile_expert, CT* __restrict__ C, int N, int K) {
+              const int* __restrict__ tile_expert, CT* __restrict__ C, int N, int K, int act, float limit, float alpha) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);     // full[STAGES], empty[STAGES], done
@@ -103,8 +103,14 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
                         float y[16];
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float g = __uint_as_float(v[i]), u = __uint_as_float(v[16 + i]);
-                            y[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+                            float g = __uint_as_float(v[i]), u = __uint_as_float(v[16 + i]);
+                            if (act == BW_ACT_CLAMPED_SWISH) {   // g sigmoid(alpha g) (u + 1) on clamped g and u
+                                g = fminf(g, limit);
+                                u = fminf(fmaxf(u, -limit), limit) + 1.f;
+                                y[i] = __fdividef(g, 1.f + __expf(-alpha * g)) * u;
+                            } else {
+                                y[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+                            }
                         }
                         bf16* dst = (bf16*)C + row * F + f0;
                         if ((F & 7) == 0) {
@@ -146,11 +152,11 @@ bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, int
 
 template <bool GATED, typename CT>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const int* tile_expert, void* C, int max_tiles, int N, int K,
-           cudaStream_t s) {
+           int act, float limit, float alpha, cudaStream_t s) {
     static bool raised[bw::MAX_DEVICES] = {};
     if (cudaError_t e = bw::allow_dynamic_smem(moe_tc_kernel<GATED, CT>, SMEM_BYTES, raised); e != cudaSuccess) return (int)e;
     bw::launch((moe_tc_kernel<GATED, CT>), dim3((N + BN - 1) / BN, max_tiles), dim3(THREADS), SMEM_BYTES, s, ta, tb, tile_expert,
-               (CT*)C, N, K);
+               (CT*)C, N, K, act, limit, alpha);
     BW_LAUNCH_CHECK();
     return 0;
 }
@@ -164,19 +170,20 @@ BW_EXPORT int bw_moe_tc_supported(const void* A, const void* W, int N, int K, in
 }
 
 // A: bfloat16 [max_tiles * 128, K]; W: bfloat16 [E, N, K]; tile_expert: int32 [max_tiles].
-// gated: W's rows alternate 16 gate / 16 up and C is bfloat16 [rows, N / 2] = silu(gate) * up;
-// else C is [rows, N] of c_type.
+// gated: W's rows alternate 16 gate / 16 up and C is bfloat16 [rows, N / 2] = glu(gate, up) with the gated
+// activation `act` of common.cuh and its limit and alpha (BW_ACT_SILU: silu(gate) * up); else C is [rows, N] of c_type.
 BW_EXPORT int bw_moe_gemm_tc(const void* A, const void* W, int gated, const int* tile_expert, void* C, int c_type,
-                             int max_tiles, int E, int N, int K, void* stream) {
+                             int max_tiles, int E, int N, int K, int act, float limit, float alpha, void* stream) {
     if (max_tiles <= 0) return 0;
     if (E <= 0 || !bw_moe_tc_supported(A, W, N, K, gated)) return BW_ERR_UNSUPPORTED;
     if (gated && c_type != BW_BF16) return BW_ERR_BAD_ARG;
     CUtensorMap ta, tb;
     if (!make_map(&ta, A, (long long)max_tiles * BM, K, BM) || !make_map(&tb, W, (long long)E * N, K, BN)) return BW_ERR_DRIVER;
     cudaStream_t s = (cudaStream_t)stream;
-    if (gated) return launch<true, bf16>(ta, tb, tile_expert, C, max_tiles, N, K, s);
-    if (c_type == BW_F32) return launch<false, float>(ta, tb, tile_expert, C, max_tiles, N, K, s);
-    if (c_type == BW_BF16) return launch<false, bf16>(ta, tb, tile_expert, C, max_tiles, N, K, s);
+    if (gated && act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH) return BW_ERR_BAD_ARG;
+    if (gated) return launch<true, bf16>(ta, tb, tile_expert, C, max_tiles, N, K, act, limit, alpha, s);
+    if (c_type == BW_F32) return launch<false, float>(ta, tb, tile_expert, C, max_tiles, N, K, 0, 0.f, 1.f, s);
+    if (c_type == BW_BF16) return launch<false, bf16>(ta, tb, tile_expert, C, max_tiles, N, K, 0, 0.f, 1.f, s);
     return BW_ERR_BAD_ARG;
 }
 

@@ -89,7 +89,112 @@ qk_norm_rope_kernel(const float* __restrict__ qkv, const int* __restrict__ posit
     }
 }
 
+// The same with the norm taken per HEAD: every query head of dq channels is divided by its own root mean
+// square and multiplied by q_gain [dq], one gain vector shared by all heads (k_gain [dq] for the key heads);
+// a null gain: no norm on that side.  After norm and rotation the queries of a token at position p are
+// multiplied by  1 + q_coef * ln(floor((p + 1) / q_every) + 1)  (q_coef == 0: by nothing), a temperature that
+// grows with the logarithm of the position.  Rows of qkv are `ld` floats apart and hold the queries first,
+// then (has_kv != 0) keys and values; whatever follows in the row (a gate's projection) is not touched.
+// has_kv == 0: a run that reads another run's keys and values projects none.  One block per token, one warp
+// per head at a time; all arithmetic float32.
+template <typename OT>
+__global__ void __launch_bounds__(256)
+head_norm_rope_kernel(const float* __restrict__ qkv, long long ld, const int* __restrict__ positions,
+                      const int* __restrict__ req_of_token, const int* __restrict__ block_table, int max_blocks,
+                      const float* __restrict__ table, int rotary_dim, int interleaved,
+                      const float* __restrict__ q_gain, const float* __restrict__ k_gain, float eps,
+                      float q_coef, float q_every,
+                      OT* __restrict__ q_out, OT* __restrict__ k_pages, OT* __restrict__ v_pages,
+                      int nh, int nkv, int dq, int dv, int dpad, int page_size, int num_pages, int has_kv) {
+    BW_PDL_TRIGGER();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int nq = nh * dq, nk = nkv * dq;
+    const int pos = positions[t];
+    int page = -1;
+    const int slot = pos % page_size;
+    if (has_kv && num_pages > 0) {
+        page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
+        if (page >= num_pages) page = -1;
+    }
+    float q_mult = 1.f;
+    if (q_coef != 0.f) q_mult = 1.f + q_coef * logf((float)floor((double)(pos + 1) / (double)q_every) + 1.f);
+    BW_PDL_WAIT();
+    const float* row = qkv + (size_t)t * ld;
+    const int half = rotary_dim >> 1;
+    const float* tab = rotary_dim ? table + (size_t)t * rotary_dim : nullptr;
+    const int n_heads = nh + (has_kv ? nkv : 0);
+    for (int h = warp; h < n_heads; h += nwarps) {
+        const bool is_q = h < nh;
+        if (!is_q && page < 0) continue;
+        const float* src = is_q ? row + (size_t)h * dq : row + nq + (size_t)(h - nh) * dq;
+        const float* gain = is_q ? q_gain : k_gain;
+        float r = 1.f;
+        if (gain) {
+            float ss = 0.f;
+            for (int c = lane; c < dq; c += 32) { const float v = src[c]; ss = fmaf(v, v, ss); }
+            r = rsqrtf(bw::warp_sum(ss) / (float)dq + eps);
+        }
+        const float mult = is_q ? q_mult : 1.f;
+        OT* dst = is_q ? q_out + ((size_t)t * nh + h) * dpad
+                       : k_pages + (((size_t)page * nkv + (h - nh)) * page_size + slot) * dpad;
+        for (int c = lane; c < dpad; c += 32) {
+            float o = 0.f;
+            if (c < dq) {
+                float x = src[c] * r;
+                if (gain) x *= gain[c];
+                o = x;
+                if (c < rotary_dim) {
+                    int j, pc; bool first;
+                    if (interleaved) { j = c >> 1; pc = c ^ 1; first = !(c & 1); }
+                    else { first = c < half; j = first ? c : c - half; pc = first ? c + half : c - half; }
+                    float y = src[pc] * r;
+                    if (gain) y *= gain[pc];
+                    const float cs = tab[j], sn = tab[half + j];
+                    o = first ? x * cs - y * sn : x * cs + y * sn;
+                }
+                o *= mult;
+            }
+            dst[c] = bw::from_f32<OT>(o);
+        }
+    }
+    if (page >= 0) {
+        const float* vsrc = row + nq + nk;
+        for (int idx = threadIdx.x; idx < nkv * dpad; idx += blockDim.x) {
+            const int h = idx / dpad, c = idx - h * dpad;
+            const float o = c < dv ? vsrc[(size_t)h * dv + c] : 0.f;
+            v_pages[(((size_t)page * nkv + h) * page_size + slot) * dpad + c] = bw::from_f32<OT>(o);
+        }
+    }
+}
+
 }  // namespace
+
+// The per-head form (head_norm_rope_kernel).  ld: floats between rows of qkv; q_gain / k_gain: float32 [dq] or
+// null; q_coef, q_every: the queries' temperature (q_coef == 0: none; q_every > 0); has_kv == 0: the rows hold
+// no keys and values and nothing is appended.
+BW_EXPORT int bw_head_norm_rope_append(const float* qkv, long long ld, const int* positions, const int* req_of_token,
+                                       const int* block_table, int max_blocks, const float* table, int rotary_dim,
+                                       int interleaved, const float* q_gain, const float* k_gain, float eps,
+                                       float q_coef, float q_every, void* q_out, void* k_pages, void* v_pages,
+                                       int out_type, int T, int nh, int nkv, int dq, int dv, int dpad, int page_size,
+                                       int num_pages, int has_kv, void* stream) {
+    if (T <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > dq || (rotary_dim & 1) || dq <= 0 || dv <= 0 || dpad < dq || dpad < dv ||
+        nh <= 0 || nkv <= 0 || page_size <= 0 || (rotary_dim > 0 && !table) || (q_coef != 0.f && !(q_every > 0.f)) ||
+        ld < (long long)nh * dq + (has_kv ? (long long)nkv * (dq + dv) : 0))
+        return BW_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+#define BW_HN(OT) bw::launch((head_norm_rope_kernel<OT>), dim3(T), dim3(256), 0, s, qkv, ld, positions, req_of_token, block_table, \
+        max_blocks, table, rotary_dim, interleaved, q_gain, k_gain, eps, q_coef, q_every, (OT*)q_out, (OT*)k_pages, (OT*)v_pages, \
+        nh, nkv, dq, dv, dpad, page_size, num_pages, has_kv)
+    if (out_type == BW_F32) BW_HN(float);
+    else if (out_type == BW_BF16) BW_HN(bf16);
+    else return BW_ERR_BAD_ARG;
+#undef BW_HN
+    BW_LAUNCH_CHECK();
+    return 0;
+}
 
 // out_type: element type of q_out and the pages.  num_pages <= 0: nothing is appended (a run that reads
 // another run's cache).  q_gain / k_gain: float32 gains of the norm, or null for no norm.

@@ -132,6 +132,28 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Ten
     return out
 
 
+def embed_positions(table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                    copies: int = 1, scale: float = 1.0) -> torch.Tensor:
+    """float32 [T, copies * H]: ``table[ids] * scale`` plus, with ``inv_freq`` (float32 [ceil(H / 2)]), a vector of the
+    token's position (entry 2i: sin(pos * inv_freq[i]), entry 2i + 1: the cosine), written ``copies`` times side by
+    side: the start of a residual stream that is kept as several copies."""
+    _dev(table, "table"); _dev(ids, "ids", torch.int32); _dev(positions, "positions", torch.int32)
+    V, H = table.shape
+    T = ids.numel()
+    if inv_freq is not None:
+        _dev(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != (H + 1) // 2:
+            raise KernelError("embed_positions: inv_freq must have ceil(H / 2) entries")
+    if positions.numel() != T or copies < 1:
+        raise KernelError("embed_positions: one position per token, at least one copy")
+    out = torch.empty((T, copies * H), dtype=torch.float32, device=table.device)
+    fn = _fn("elementwise", "bw_embed_positions",
+             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(table), _code(table, "table"), _ptr(ids), _ptr(positions), _ptr(inv_freq), _ptr(out), T, H, V, float(scale),
+              int(copies), _stream()), "embed_positions")
+    return out
+
+
 def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[float] = None) -> torch.Tensor:
     """In place on float32 ``logits``: times ``scale``, then ``softcap * tanh(x / softcap)`` if a cap is given."""
     _dev(logits, "logits", torch.float32)
@@ -284,6 +306,47 @@ def swiglu(gu: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.T
     return out
 
 
+ACT_SILU, ACT_CLAMPED_SWISH, ACT_RELU2 = 0, 1, 2   # the activation codes of csrc/common.cuh
+GATED_ACTIVATIONS = {"silu": ACT_SILU, "clamped_swish": ACT_CLAMPED_SWISH}
+UNARY_ACTIVATIONS = {"relu2": ACT_RELU2}
+
+
+def glu(gu: torch.Tensor, act: int, limit: float = 0.0, alpha: float = 1.0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """[T, 2I] (gate | up) -> [T, I]: ACT_SILU ``silu(gate) * up``; ACT_CLAMPED_SWISH, with g = min(gate, limit) and
+    u = clamp(up, -limit, limit): ``g * sigmoid(alpha * g) * (u + 1)``.  Float32 arithmetic."""
+    _dev(gu, "gate_up")
+    T, I2 = gu.shape
+    if I2 % 2:
+        raise KernelError("glu: input width must be even (gate | up)")
+    out = torch.empty((T, I2 // 2), dtype=out_dtype or gu.dtype, device=gu.device)
+    fn = _fn("elementwise", "bw_glu", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(gu), _code(gu, "gate_up"), _ptr(out), _code(out, "out"), T, I2 // 2, int(act), float(limit), float(alpha),
+              _stream()), "glu")
+    return out
+
+
+def unary_act(x: torch.Tensor, act: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """Element by element: ACT_RELU2 ``max(x, 0) ** 2`` (float32 arithmetic)."""
+    _dev(x, "x")
+    out = torch.empty(x.shape, dtype=out_dtype or x.dtype, device=x.device)
+    fn = _fn("elementwise", "bw_unary_act", [c_void_p, c_int, c_void_p, c_int, c_ll, c_int, c_void_p])
+    _check(fn(_ptr(x), _code(x, "x"), _ptr(out), _code(out, "out"), x.numel(), int(act), _stream()), "unary_act")
+    return out
+
+
+def sigmoid_gate(o: torch.Tensor, g: torch.Tensor, nh: int, dv: int) -> torch.Tensor:
+    """In place: ``o[t, h, c] *= sigmoid(g[t, h * dv + c])`` for c < dv; o is [T, nh * dpad] with dpad >= dv
+    (channels beyond dv become zero); g float32 [T, nh * dv], possibly a column range of a wider tensor."""
+    _dev(o, "o"); _dev(g, "g", torch.float32, contiguous=False)
+    T = o.shape[0]
+    dpad = o.shape[1] // nh
+    if o.shape[1] != nh * dpad or dpad < dv or g.shape != (T, nh * dv) or g.stride(1) != 1:
+        raise KernelError("sigmoid_gate: o must be [T, nh * dpad], g [T, nh * dv] with contiguous rows")
+    fn = _fn("elementwise", "bw_sigmoid_gate", [c_void_p, c_int, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(o), _code(o, "o"), _ptr(g), g.stride(0), T, nh, dv, dpad, _stream()), "sigmoid_gate")
+    return o
+
+
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, magnitude: float = 1.0) -> torch.Tensor:
     """cos and sin of ``pos * inv_freq`` per token, times ``magnitude``: float32 [T, rotary_dim] (cos, then sin)."""
     _dev(positions, "positions", torch.int32); _dev(inv_freq, "inv_freq", torch.float32)
@@ -393,8 +456,10 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
 
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
                    req_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, window: Optional[int],
-                   scale: float, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None) -> torch.Tensor:
+                   scale: float, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                   sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(q, "q"); _dev(k_pages, "k_pages", q.dtype); _dev(v_pages, "v_pages", q.dtype)
+    _check_sink(sink, nh)
     _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
@@ -405,11 +470,18 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         out = torch.empty_like(q)
     fn = _fn("attention_simt", "bw_attention_simt",
              [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q, "q"), _ptr(positions), _ptr(req_of_token),
               _ptr(block_table), block_table.shape[1], _ptr(out), T, nh, nkv, hd, page_size, num_pages,
-              int(window or 0), int(chunk or 0), float(scale), _stream()), "attention_simt")
+              int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _stream()), "attention_simt")
     return out
+
+
+def _check_sink(sink: Optional[torch.Tensor], nh: int) -> None:
+    if sink is not None:
+        _dev(sink, "sink", torch.float32)
+        if sink.numel() != nh:
+            raise KernelError(f"attention: the sink must have one float32 entry per query head ({nh})")
 
 
 # ------------------------------------------------------------------ sampling
@@ -675,25 +747,26 @@ def attention_takes_unrotated(hd: int, page_size: int) -> bool:
 
 def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                     block_table: torch.Tensor, nh: int, window: Optional[int], scale: float,
-                    chunk: Optional[int] = None) -> torch.Tensor:
+                    chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
     holds this step's keys and values, unless ``q`` is an :class:`UnrotatedQKV`).  float32: the
     CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size.  A query sees the keys
     from ``first_visible(position, window, chunk)`` on: the latest ``window`` keys, and none before the
-    start of its own block of ``chunk`` positions (blocks are counted from position 0)."""
+    start of its own block of ``chunk`` positions (blocks are counted from position 0).  ``sink`` (float32, one
+    entry per query head): the softmax of a row has one more term exp(sink) that has no key and no value."""
     if isinstance(q, UnrotatedQKV):
         if batch.T == batch.R and attention_takes_unrotated(k_pages.shape[3], k_pages.shape[2]):
-            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk)
+            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink)
         q = q.materialise()
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                              window, scale, chunk=chunk)
-    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk)
+                              window, scale, chunk=chunk, sink=sink)
+    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink)
 
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p]
+                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
 
 
 _sm_counts = {}
@@ -781,8 +854,10 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
 
 
 def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
-                  nh: int, window: Optional[int], scale: float, chunk: Optional[int] = None) -> torch.Tensor:
+                  nh: int, window: Optional[int], scale: float, chunk: Optional[int] = None,
+                  sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
+    _check_sink(sink, nh)
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
     raw = q if isinstance(q, UnrotatedQKV) else None
@@ -821,7 +896,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros=attention_tc_macros(hd))
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
                   _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
-                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _stream()), "attention_tc")
+                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _stream()), "attention_tc")
         n_rows = 0
         if not n_keys:
             return out
@@ -833,11 +908,11 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
               _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
               raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
               raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, merge_max,
-              _stream()), "attention_mma")
+              _ptr(sink), _stream()), "attention_mma")
     return out
 
 
-_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
 
 
 def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:
@@ -965,6 +1040,87 @@ def qk_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, tab
     return q_out
 
 
+def head_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, table: Optional[torch.Tensor],
+                          rotary_dim: int, interleaved: bool, q_gain: Optional[torch.Tensor],
+                          k_gain: Optional[torch.Tensor], eps: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                          nh: int, nkv: int, dq: int, dv: int, has_kv: bool = True, append: bool = True,
+                          q_temp: Optional[tuple] = None) -> torch.Tensor:
+    """:func:`qk_norm_rope_append` with the norm taken per head: every query head is divided by its own root mean
+    square and multiplied by ``q_gain`` (float32 [dq], shared by the heads; ``k_gain`` for the key heads).
+    ``qkv`` float32 [T, >= nh*dq (+ nkv*dq + nkv*dv with ``has_kv``)]: further columns (a gate's projection) are
+    left alone.  ``q_temp`` = (coef, every): after norm and rotation the queries of a token at position p are
+    multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``.  Without ``has_kv`` (a run that reads another
+    run's keys and values) nothing is appended."""
+    _dev(qkv, "qkv", torch.float32); _dev(block_table, "block_table", torch.int32)
+    _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)
+    T = qkv.shape[0]
+    num_pages, pk, page_size, dpad = k_pages.shape
+    need = nh * dq + (nkv * (dq + dv) if has_kv else 0)
+    if qkv.shape[1] < need or pk != nkv or v_pages.shape != k_pages.shape:
+        raise KernelError("head_norm_rope_append: qkv must be [T, >= nh*dq (+ nkv*dq + nkv*dv)], pages [num_pages, nkv, page, dpad]")
+    for name, g in (("q_gain", q_gain), ("k_gain", k_gain)):
+        if g is not None:
+            _dev(g, name, torch.float32)
+            if g.numel() != dq:
+                raise KernelError(f"head_norm_rope_append: {name} must have {dq} entries")
+    if rotary_dim:
+        _dev(table, "table", torch.float32)
+        if tuple(table.shape) != (T, rotary_dim):
+            raise KernelError("head_norm_rope_append: the cos/sin table must be [T, rotary_dim]")
+    coef, every = (float(q_temp[0]), float(q_temp[1])) if q_temp is not None else (0.0, 1.0)
+    q_out = torch.empty((T, nh * dpad), dtype=k_pages.dtype, device=qkv.device)
+    fn = _fn("qk_norm_rope", "bw_head_norm_rope_append",
+             [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float,
+              c_float, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_void_p])
+    _check(fn(_ptr(qkv), qkv.stride(0), _ptr(batch.positions), _ptr(batch.req_of_token), _ptr(block_table),
+              block_table.shape[1], _ptr(table), int(rotary_dim), int(interleaved), _ptr(q_gain), _ptr(k_gain), float(eps),
+              coef, every, _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(k_pages, "pages"), T, nh, nkv, dq, dv, dpad,
+              page_size, num_pages if (append and has_kv) else 0, int(has_kv), _stream()), "head_norm_rope_append")
+    return q_out
+
+
+# ------------------------------------------------------------------ several copies of the stream (hyper-connections)
+
+HC_MAX_STREAMS = 8   # the most copies of the stream that hc_step takes (csrc/hyper.cu is built for 1 to 8)
+
+
+def hc_step(streams: torch.Tensor, S: int, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+            out_w: Optional[torch.Tensor] = None, in_w: Optional[torch.Tensor] = None,
+            gain: Optional[torch.Tensor] = None, eps: float = 0.0, rows: Optional[torch.Tensor] = None,
+            out_dtype: torch.dtype = torch.float32) -> Optional[torch.Tensor]:
+    """One step of a stream kept as ``S`` copies (``streams`` float32 [T, S * H], updated in place):
+
+        with ``y`` [T, H]:   x_t <- sum_s mix[s, t] x_s + out_w[t] * y      (all copies at once, from the old ones)
+        with ``in_w`` [S]:   returns norm(sum_s in_w[s] x_s) for the next sublayer, the norm being
+                             u / sqrt(mean(u^2) + eps) * gain (float32 [H]); without ``gain`` the sum itself, float32.
+
+    ``rows``: only those rows are computed and ``streams`` is left as it is (the last read of a model)."""
+    _dev(streams, "streams", torch.float32)
+    T = streams.shape[0]
+    H = streams.shape[1] // S
+    if streams.shape[1] != S * H:
+        raise KernelError("hc_step: streams must be [T, S * H]")
+    for name, t, n in (("y", y, T * H), ("mix", mix, S * S), ("out_w", out_w, S), ("in_w", in_w, S), ("gain", gain, H)):
+        if t is not None:
+            _dev(t, name, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"hc_step: {name} must have {n} float32 entries")
+    if y is not None and (mix is None or out_w is None):
+        raise KernelError("hc_step: a write needs mix and out_w")
+    n = T
+    if rows is not None:
+        _dev(rows, "rows", torch.int32)
+        n = rows.numel()
+    out = None
+    if in_w is not None:
+        out = torch.empty((n, H), dtype=out_dtype if gain is not None else torch.float32, device=streams.device)
+    fn = _fn("hyper", "bw_hc_step", [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    _check(fn(_ptr(streams), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(gain), _ptr(rows), _ptr(out),
+              _code(out, "out") if out is not None else F32, n, S, H, float(eps), int(rows is None and y is not None),
+              _stream()), "hc_step")
+    return out
+
+
 # ------------------------------------------------------------------ gated linear attention
 
 GLA_MAX_KEY_DIM = 256
@@ -1059,10 +1215,11 @@ def moe_gemm_tc_supports(H: int, F: int) -> bool:
 
 
 def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, gated: bool = False,
-                out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                out_dtype: Optional[torch.dtype] = None, act: int = ACT_SILU, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """The grouped product on the tensor cores: a bfloat16 [tiles * 128, K], w bfloat16 [E, N, K]; row r gets
     ``a[r] @ w[e].T`` with e the expert of r's tile.  ``gated``: w's rows alternate 16 gate rows / 16 up rows
-    (:func:`interleave_gate_up` per expert) and the result is bfloat16 [rows, N / 2] = silu(gate) * up."""
+    (:func:`interleave_gate_up` per expert) and the result is bfloat16 [rows, N / 2] = silu(gate) * up, or the
+    gated activation ``act`` with its ``limit`` and ``alpha`` (:func:`glu`)."""
     _dev(a, "a", torch.bfloat16); _dev(w, "w", torch.bfloat16); _dev(tile_expert, "tile_expert", torch.int32)
     rows, K = a.shape
     E, N, K2 = w.shape
@@ -1070,9 +1227,10 @@ def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, gat
         raise KernelError("moe_gemm_tc: a must be [tiles * 128, K], w [E, N, K]")
     out_dtype = torch.bfloat16 if gated else (out_dtype or torch.bfloat16)
     out = torch.empty((rows, N // 2 if gated else N), dtype=out_dtype, device=a.device)
-    fn = _fn("moe_tc", "bw_moe_gemm_tc", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    fn = _fn("moe_tc", "bw_moe_gemm_tc", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_float, c_float, c_void_p])
     _check(fn(_ptr(a), _ptr(w), int(gated), _ptr(tile_expert), _ptr(out), _code(out, "out"), tile_expert.numel(), E, N, K,
-              _stream()), "moe_gemm_tc")
+              int(act), float(limit), float(alpha), _stream()), "moe_gemm_tc")
     return out
 
 
@@ -1081,28 +1239,44 @@ def moe_tc_status() -> int:
     return int(_fn("moe_tc", "bw_moe_tc_status", [])())
 
 
-def moe_route(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False):
+def moe_route(logits: torch.Tensor, top: int, softmax: bool = False, renormalize: bool = False,
+              bias: Optional[torch.Tensor] = None, renorm_eps: float = 0.0):
     """float32 router logits [T, E] -> (chosen experts int32 [T, top], their weights float32 [T, top]):
     scores are sigmoid(logit) (or the softmax over the experts), the ``top`` largest are chosen (lowest
-    index on ties) in falling order, optionally renormalised to sum 1."""
+    index on ties) in falling order, optionally renormalised to sum 1 (divided by their sum + ``renorm_eps``).
+    ``bias`` (float32 [E]): the choice goes by score + bias, the weights stay the scores."""
     _dev(logits, "logits", torch.float32)
     T, E = logits.shape
+    _check_route_bias(bias, E)
     sel = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    fn = _fn("moe", "bw_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
-    _check(fn(_ptr(logits), T, E, int(top), int(softmax), int(renormalize), _ptr(sel), _ptr(wt), _stream()), "moe_route")
+    fn = _fn("moe", "bw_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(logits), T, E, int(top), int(softmax), int(renormalize), _ptr(bias), float(renorm_eps), _ptr(sel), _ptr(wt),
+              _stream()), "moe_route")
     return sel, wt
+
+
+def _check_route_bias(bias: Optional[torch.Tensor], E: int) -> None:
+    if bias is not None:
+        _dev(bias, "bias", torch.float32)
+        if bias.numel() != E:
+            raise KernelError(f"moe_route: the bias must have one float32 entry per router output ({E})")
 
 
 MOE_FUSED_FRONT_MAX_ROWS = 128   # up to this many (token, choice) rows one block routes, plans and regroups (the kernel takes 1,024)
 
 
 def moe_route_plan_scatter(logits: torch.Tensor, x: torch.Tensor, top: int, tile_rows: int, softmax: bool = False,
-                           renormalize: bool = False, scale_input: bool = False):
+                           renormalize: bool = False, scale_input: bool = False, experts: Optional[int] = None,
+                           bias: Optional[torch.Tensor] = None, renorm_eps: float = 0.0):
     """:func:`moe_route`, :func:`moe_plan` and :func:`moe_scatter` as one kernel, for steps of few tokens.
-    Returns (weights [T, top], place of every (token, choice), expert of every tile, the regrouped operand)."""
+    Returns (weights [T, top], place of every (token, choice), expert of every tile, the regrouped operand).
+    ``experts``: how many of the router's outputs are experts with weights (default: all); a choice beyond
+    them has no place (-1)."""
     _dev(logits, "logits", torch.float32); _dev(x, "x")
-    T, E = logits.shape
+    T, E_total = logits.shape
+    E = E_total if experts is None else int(experts)
+    _check_route_bias(bias, E_total)
     H = x.shape[1]
     n = T * top
     if n > MOE_FUSED_FRONT_MAX_ROWS or x.shape[0] != T:
@@ -1114,9 +1288,11 @@ def moe_route_plan_scatter(logits: torch.Tensor, x: torch.Tensor, top: int, tile
     pos_of = torch.empty(n, dtype=torch.int32, device=dev)
     tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=dev)
     xs = torch.empty((max_tiles * tile_rows, H), dtype=x.dtype, device=dev)
-    fn = _fn("moe", "bw_moe_route_plan_scatter", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+    fn = _fn("moe", "bw_moe_route_plan_scatter", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p,
+                                                  c_void_p, c_int, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
-    _check(fn(_ptr(logits), T, E, int(top), int(softmax), int(renormalize), _ptr(sel), _ptr(wt), int(tile_rows), max_tiles,
+    _check(fn(_ptr(logits), T, E, E_total, int(top), int(softmax), int(renormalize), _ptr(bias), float(renorm_eps), _ptr(sel), _ptr(wt),
+              int(tile_rows), max_tiles,
               _ptr(pos_of), _ptr(tile_expert), _ptr(x), _code(x, "x"), _ptr(xs), H, int(scale_input), _stream()),
            "moe_route_plan_scatter")
     return wt, pos_of, tile_expert, xs
@@ -1124,7 +1300,8 @@ def moe_route_plan_scatter(logits: torch.Tensor, x: torch.Tensor, top: int, tile
 
 def moe_plan(sel: torch.Tensor, experts: int, tile_rows: Optional[int] = None):
     """(row of every (token, choice) in the regrouped order int32 [T * top], expert of every tile of
-    ``tile_rows`` rows int32 [max_tiles], -1 for idle tiles)."""
+    ``tile_rows`` rows int32 [max_tiles], -1 for idle tiles).  A choice that names no expert below ``experts``
+    (an expert without weights) gets no row: -1."""
     _dev(sel, "sel", torch.int32)
     n = sel.numel()
     tile_rows = tile_rows or moe_tile_rows()
@@ -1149,9 +1326,10 @@ def moe_scatter(x: torch.Tensor, pos_of: torch.Tensor, wt: torch.Tensor, rows: i
 
 
 def moe_gemm(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, w2: Optional[torch.Tensor] = None,
-             out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+             out_dtype: Optional[torch.dtype] = None, act: int = ACT_SILU, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """Row r of the result is ``a[r] @ w[e].T`` with e the expert of r's tile; with ``w2`` it is
-    ``silu(a[r] @ w[e].T) * (a[r] @ w2[e].T)``.  a [rows, K], w (w2) [E, N, K]."""
+    ``silu(a[r] @ w[e].T) * (a[r] @ w2[e].T)``, or the gated activation ``act`` (:func:`glu`) of the two.
+    a [rows, K], w (w2) [E, N, K]."""
     _dev(a, "a"); _dev(w, "w", a.dtype); _dev(tile_expert, "tile_expert", torch.int32)
     if w2 is not None:
         _dev(w2, "w2", a.dtype)
@@ -1162,16 +1340,19 @@ def moe_gemm(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, w2: Op
     if K != K2 or rows != tile_expert.numel() * moe_tile_rows():
         raise KernelError("moe_gemm: a must be [tiles * tile rows, K], w [E, N, K]")
     out = torch.empty((rows, N), dtype=out_dtype or a.dtype, device=a.device)
-    fn = _fn("moe", "bw_moe_gemm", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    fn = _fn("moe", "bw_moe_gemm", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                    c_float, c_float, c_void_p])
     _check(fn(_ptr(a), _ptr(w), _ptr(w2), _code(a, "a"), _ptr(tile_expert), _ptr(out), _code(out, "out"),
-              tile_expert.numel(), N, K, _stream()), "moe_gemm")
+              tile_expert.numel(), N, K, int(act), float(limit), float(alpha), _stream()), "moe_gemm")
     return out
 
 
 def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, wt: torch.Tensor, out: torch.Tensor, scale_output: bool,
-                mode: str = "write", gain: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
+                mode: str = "write", gain: Optional[torch.Tensor] = None, eps: float = 0.0,
+                x: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out[t]`` (= | +=) the sum over t's choices, in order, of (weight *) ``y[pos_of[t * top + k]]``;
-    mode "norm_add": the sum is divided by its root mean square, multiplied by ``gain`` and added."""
+    mode "norm_add": the sum is divided by its root mean square, multiplied by ``gain`` and added.
+    ``x`` [T, H]: what a choice without a place (``pos_of`` < 0: an expert that returns its input) contributes."""
     _dev(y, "y", torch.float32); _dev(pos_of, "pos_of", torch.int32); _dev(wt, "wt", torch.float32)
     _dev(out, "out", torch.float32)
     T, H = out.shape
@@ -1180,8 +1361,12 @@ def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, wt: torch.Tensor, out: to
         raise KernelError("moe_combine: bad mode or shapes")
     if gain is not None:
         gain = _dev(gain, "gain", torch.float32)
+    if x is not None:
+        _dev(x, "x")
+        if x.shape != (T, H):
+            raise KernelError("moe_combine: x must be [T, H]")
     fn = _fn("moe", "bw_moe_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
-                                       c_float, c_void_p])
+                                       c_float, c_void_p, c_int, c_void_p])
     _check(fn(_ptr(y), _ptr(pos_of), _ptr(wt), pos_of.numel() // max(T, 1), int(scale_output), _ptr(out), T, H, modes[mode],
-              _ptr(gain), float(eps), _stream()), "moe_combine")
+              _ptr(gain), float(eps), _ptr(x), _code(x, "x") if x is not None else F32, _stream()), "moe_combine")
     return out

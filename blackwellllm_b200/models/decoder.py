@@ -2,7 +2,10 @@
 built from the configuration's layer specs, a schedule that says in which order
 they run and whose cache each run uses, a final norm and the output head; around
 them the configuration's optional constants (embedding multiplier, logit scale,
-logit soft cap).
+logit soft cap), an optional vector of the position added to the embedding, and an
+optional stream that is kept as several copies (``ModelConfig.streams``: every block
+is then a "hyper" block, the stream is [T, streams * hidden], and the model's last
+norm reads the sum of the copies).
 
 It is driven by :class:`ModelConfig` alone and knows no architecture by name.
 Reference for the sequence of operations: src/core/engine.cpp:921-1041.
@@ -16,7 +19,14 @@ import torch
 from ..config.specs import ModelConfig
 from ..kernels import ops
 from ..parts import BuildContext, ParamSpec, build_block, build_norm
+from ..parts.block import flush_hyper_write
 from ..parts.linear import Linear
+
+
+def sinusoid_frequencies(width: int, base: float) -> torch.Tensor:
+    """float32 [ceil(width / 2)]: base^(-2i / width), computed in float64 and rounded once."""
+    i = torch.arange((width + 1) // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / width).to(torch.float32)
 
 
 class DecoderModel:
@@ -36,6 +46,21 @@ class DecoderModel:
         self.embed: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self._keeps_embedding = any(e.add_embedding for e in config.schedule)
+        self.streams = config.streams          # None: one plain stream
+        if self.streams is not None:
+            if any(ls.block != "hyper" for ls in config.layers) or self._keeps_embedding:
+                raise ValueError("a stream kept as several copies needs 'hyper' blocks throughout and no repeated stretch")
+            if not hasattr(self.final_norm, "gain_f32"):
+                raise ValueError(f"{type(self.final_norm).__name__} cannot close a stream of several copies (it has no gain_f32)")
+            self._ones = torch.ones(self.streams, dtype=torch.float32, device=ctx.device)
+        elif any(ls.block == "hyper" for ls in config.layers):
+            raise ValueError("'hyper' blocks need ModelConfig.streams")
+        self._pos_freq = None
+        pe = config.position_embedding
+        if pe is not None:
+            if getattr(pe, "kind", None) != "sinusoidal":
+                raise ValueError(f"unknown position embedding {pe!r}")
+            self._pos_freq = sinusoid_frequencies(H, pe.base).to(ctx.device)
         # called as stream_hook(schedule position, stream [T, H] float32) after every run of a layer, if set:
         # for looking at the stream layer by layer (the engine then runs uncaptured; see Engine.step)
         self.stream_hook = None
@@ -81,7 +106,12 @@ class DecoderModel:
         [len(batch.logit_rows), vocab] for the rows that were asked for."""
         c = self.config
         ops.discard_pending()   # nothing of an earlier (failed) pass is added into this one's tensors
-        h = ops.embed_gather(self.embed, batch.token_ids, scale=c.embedding_multiplier)
+        S = self.streams
+        if S is not None or self._pos_freq is not None:
+            h = ops.embed_positions(self.embed, batch.token_ids, batch.positions, self._pos_freq, copies=S or 1,
+                                    scale=c.embedding_multiplier)
+        else:
+            h = ops.embed_gather(self.embed, batch.token_ids, scale=c.embedding_multiplier)
         h0 = h.clone() if self._keeps_embedding else None   # the embedding's output, for repeated passes
         for pos, e in enumerate(self.config.schedule):
             cache = caches[e.cache_of if e.cache_of is not None else pos]
@@ -93,14 +123,25 @@ class DecoderModel:
             blk.forward(h, batch, cache, owns_cache=e.cache_of is None)
             if self.stream_hook is not None:
                 ops.resolve_pending()
-                self.stream_hook(pos, h)
+                if S is not None:   # the hook sees the sum of the copies
+                    flush_hyper_write(h, batch, S)
+                    self.stream_hook(pos, ops.hc_step(h, S, in_w=self._ones))
+                else:
+                    self.stream_hook(pos, h)
         n = batch.logit_rows.numel()
         if n == 0:
             ops.discard_pending(h)
+            batch.extras.pop("hc_write", None)
             return torch.empty((0, self.config.vocab_size), dtype=torch.float32, device=h.device)
-        if not self.final_norm.adds_pending:
-            ops.resolve_pending()
-        x = self.final_norm.forward(h, rows=batch.logit_rows)
+        if S is not None:
+            # the last block's write, the sum of the copies and the model's norm, on the wanted rows only
+            y, mix, out_w = batch.extras.pop("hc_write", None) or (None, None, None)
+            x = ops.hc_step(h, S, y, mix, out_w, in_w=self._ones, gain=self.final_norm.gain_f32(), eps=self.final_norm.eps,
+                            rows=batch.logit_rows, out_dtype=self.ctx.dtype)
+        else:
+            if not self.final_norm.adds_pending:
+                ops.resolve_pending()
+            x = self.final_norm.forward(h, rows=batch.logit_rows)
         ops.discard_pending(h)          # the stream ends here: only the chosen rows were summed
         logits = self.head(x, out_dtype=torch.float32)
         if c.logit_scale != 1.0 or c.logit_softcap is not None:

@@ -17,6 +17,14 @@ whole key projection before the rotation), an explicit ``softmax_scale``, and ``
 that call the tensors otherwise.  With any of the first three, or an encoding that has no fused
 projection, the route is: projection (float32 out) -> one kernel that norms, rotates and appends
 (``PositionEncoding.norm_rotate_append``) -> attention -> output projection.
+
+Further options, each of which takes that route too: ``qk_norm = "head"`` (every query and key head normed by
+itself, one gain vector of the head's size shared by the heads), ``q_temperature`` (the queries of position p
+times 1 + coef ln(floor((p + 1) / every) + 1)), ``sink`` (one learned number per query head whose exponential
+joins the softmax's denominator: the kernels add it when they normalise a row), ``output_gate`` (the heads'
+outputs times sigmoid(W_g x) before the output projection; W_g's rows ride in the q/k/v product), and
+``shares_kv`` (no key and value tensors: the run reads the cache of the schedule entry it names, which the
+other layer filled earlier in the same step, with its own queries).
 """
 from __future__ import annotations
 
@@ -31,7 +39,7 @@ from .linear import Linear
 
 _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
                   "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+                  "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks", "g": "g_proj.weight"}
 
 
 class GQAAttention(Mixer):
@@ -45,13 +53,32 @@ class GQAAttention(Mixer):
         self.chunk = getattr(spec, "chunk", None)
         self.dv = int(getattr(spec, "v_head_dim", None) or self.hd)
         self.qk_norm_eps = getattr(spec, "qk_norm_eps", None)
+        self.norm_per_head = getattr(spec, "qk_norm", "whole") == "head"
+        if getattr(spec, "qk_norm", "whole") not in ("whole", "head"):
+            raise ValueError(f"qk_norm must be 'whole' or 'head', got {spec.qk_norm!r}")
+        qt = getattr(spec, "q_temperature", None)
+        self.q_temp = (float(qt[0]), float(qt[1])) if qt is not None and float(qt[0]) != 0.0 else None
+        if self.q_temp is not None and not self.q_temp[1] > 0:
+            raise ValueError("q_temperature needs every > 0")
+        self.has_sink = bool(getattr(spec, "sink", False))
+        self.gated = bool(getattr(spec, "output_gate", False))
+        self.shares_kv = bool(getattr(spec, "shares_kv", False))
         self.names = dict(_DEFAULT_NAMES)
         self.names.update(dict(getattr(spec, "names", ()) or ()))
         # head size of the cache and the attention kernels: both sizes fit, in steps the kernels take
         step = 16 if ctx.dtype == torch.bfloat16 else 1
         self.dpad = -(-max(self.hd, self.dv) // step) * step
-        self.general = self.qk_norm_eps is not None or self.dv != self.hd or self.dpad != self.hd
-        self.q_gain = self.k_gain = None
+        self.general = (self.qk_norm_eps is not None or self.dv != self.hd or self.dpad != self.hd or self.norm_per_head
+                        or self.q_temp is not None or self.gated or self.shares_kv)
+        # the kernel that norms per head also takes rows with a gate's columns behind q, k, v, or without k and v
+        self.per_head_route = self.norm_per_head or self.q_temp is not None or self.shares_kv
+        if self.shares_kv and self.qkv_bias:
+            raise ValueError("a mixer that shares another run's keys and values has no key and value biases")
+        if self.per_head_route and self.qk_norm_eps is not None and not self.norm_per_head:
+            raise ValueError("a query temperature or shared keys and values go with the per-head norm (or none)")
+        self.q_gain = self.k_gain = self.sink = None
+        self.gate: Linear = None
+        self.g_off = 0
         self.scale = float(spec.softmax_scale) if spec.softmax_scale is not None else self.hd ** -0.5
         self.ctx = ctx
         self.position = build_position(spec.position, self.hd, ctx)
@@ -61,25 +88,43 @@ class GQAAttention(Mixer):
         self.o: Linear = None
 
     def cache_request(self):
+        # (a run with ``shares_kv`` is never asked: its schedule entry names the run whose cache it reads)
         return PagedKVRequest(self.nkv, self.dpad, self.window)
 
     def param_specs(self) -> List[ParamSpec]:
         H, q, k, v = self.hidden_size, self.nh * self.hd, self.nkv * self.hd, self.nkv * self.dv
         n = self.names
-        specs = [ParamSpec(n["q"], (q, H)), ParamSpec(n["k"], (k, H)), ParamSpec(n["v"], (v, H)),
-                 ParamSpec(n["o"], (H, self.nh * self.dv))]
+        specs = [ParamSpec(n["q"], (q, H))]
+        if not self.shares_kv:
+            specs += [ParamSpec(n["k"], (k, H)), ParamSpec(n["v"], (v, H))]
+        specs.append(ParamSpec(n["o"], (H, self.nh * self.dv)))
         if self.qkv_bias:
             specs += [ParamSpec(n["q_bias"], (q,), role="bias", init="bias_normal"),
                       ParamSpec(n["k_bias"], (k,), role="bias", init="bias_normal"),
                       ParamSpec(n["v_bias"], (v,), role="bias", init="bias_normal")]
         if self.qk_norm_eps is not None:
-            specs += [ParamSpec(n["q_norm"], (q,), role="gain", init="ones"),
-                      ParamSpec(n["k_norm"], (k,), role="gain", init="ones")]
+            specs.append(ParamSpec(n["q_norm"], (self.hd if self.norm_per_head else q,), role="gain", init="ones"))
+            if not self.shares_kv:
+                specs.append(ParamSpec(n["k_norm"], (self.hd if self.norm_per_head else k,), role="gain", init="ones"))
+        if self.has_sink:
+            specs.append(ParamSpec(n["sink"], (self.nh,), role="bias", init="bias_normal"))
+        if self.gated:
+            specs.append(ParamSpec(n["g"], (self.nh * self.dv, H)))
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self.names
-        w = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0)
+        parts = [tensors[n["q"]]] + ([] if self.shares_kv else [tensors[n["k"]], tensors[n["v"]]])
+        if self.has_sink:
+            self.sink = tensors[n["sink"]].float().contiguous()
+        if self.gated:
+            if self.per_head_route or self.qk_norm_eps is None:
+                # the gate's rows ride in the q/k/v product; the kernel that follows leaves its columns alone
+                self.g_off = sum(p.shape[0] for p in parts)
+                parts.append(tensors[n["g"]])
+            else:
+                self.gate = Linear(tensors[n["g"]])
+        w = torch.cat(parts, dim=0)
         b = None
         if self.qkv_bias:
             bs = [tensors[n["q_bias"]], tensors[n["k_bias"]], tensors[n["v_bias"]]]
@@ -88,7 +133,7 @@ class GQAAttention(Mixer):
         wo = tensors[n["o"]]
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[n["q_norm"]].float().contiguous()
-            self.k_gain = tensors[n["k_norm"]].float().contiguous()
+            self.k_gain = None if self.shares_kv else tensors[n["k_norm"]].float().contiguous()
         if self.general:
             if self.dpad != self.dv:   # the attention's output has dpad channels a head; those beyond dv are zeros
                 wo = torch.nn.functional.pad(wo.view(wo.shape[0], self.nh, self.dv), (0, self.dpad - self.dv)) \
@@ -105,13 +150,21 @@ class GQAAttention(Mixer):
             q = self.project(x, batch, cache, owns_cache)
         else:
             qkv = self.qkv(x, out_dtype=torch.float32)
-            if self.general:
+            if self.per_head_route or (self.gated and self.gate is None):
+                q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
+                                                     self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache,
+                                                     per_head=True, q_temp=self.q_temp, has_kv=not self.shares_kv)
+            elif self.general:
                 q = self.position.norm_rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, self.dv, self.q_gain,
                                                      self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache)
             else:
                 q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
         o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
-                                self.nh, self.window, self.scale, self.chunk)
+                                self.nh, self.window, self.scale, self.chunk, self.sink)
+        if self.gated:
+            g = self.gate(x, out_dtype=torch.float32) if self.gate is not None \
+                else qkv[:, self.g_off:self.g_off + self.nh * self.dv]
+            ops.sigmoid_gate(o, g, self.nh, self.dv)
         if accumulate:
             self.o.add_to(o, residual)
         else:

@@ -99,10 +99,13 @@ class PositionEncoding(Part):
         raise NotImplementedError
 
     def norm_rotate_append(self, qkv, batch, cache, nh: int, nkv: int, dq: int, dv: int, q_gain, k_gain, eps: float,
-                           append: bool = True) -> torch.Tensor:
+                           append: bool = True, per_head: bool = False, q_temp=None, has_kv: bool = True) -> torch.Tensor:
         """The general form of :meth:`rotate_append`: qkv [T, nh*dq + nkv*dq + nkv*dv] float32; with gains,
         all query channels of a token (and all its key channels) are RMS-normed together first; the cache's
-        head size may exceed dq and dv (the rest is written as zeros)."""
+        head size may exceed dq and dv (the rest is written as zeros).  ``per_head``: every head is normed by
+        itself (gains of dq entries, shared by the heads) and qkv may have further columns, which are left
+        alone; ``q_temp`` (coef, every): the queries are multiplied by 1 + coef ln(floor((p + 1) / every) + 1);
+        ``has_kv=False``: qkv holds queries only and nothing is appended."""
         raise NotImplementedError
 
     def fuse_projection(self, weight: torch.Tensor, bias: Optional[torch.Tensor], nh: int, nkv: int, hd: int):

@@ -109,3 +109,79 @@ class SandwichBlock(PreNormBlock):
 
 register_block("prenorm", PreNormBlock)
 register_block("sandwich", SandwichBlock)
+
+
+class HyperBlock(PreNormBlock):
+    """Pre-norm sublayers over a stream that is kept as several copies (hyper-connections): sublayer q reads
+    ``u = sum_s in_q[s] x_s`` through its norm and writes ``x_t <- sum_s mix_q[s, t] x_s + out_q[t] y`` (all
+    copies at once from the old ones).  ``residual`` is float32 [T, streams * hidden].  The write of one
+    sublayer and the read and norm of the next are one kernel (``ops.hc_step``); the write of the block's
+    last sublayer is left to whoever reads the stream next (the next block, the model's last norm):
+    ``batch.extras["hc_write"]`` holds (y, mix, out) until then, and :func:`flush_hyper_write` makes it."""
+
+    def __init__(self, layer_spec, hidden_size: int, ctx: BuildContext):
+        super().__init__(layer_spec, hidden_size, ctx)
+        hc = layer_spec.hyper
+        if hc is None:
+            raise ValueError("the hyper arrangement needs the layer's hyper-connection description")
+        self.S = int(hc.streams)
+        if not 1 <= self.S <= ops.HC_MAX_STREAMS:
+            raise ValueError(f"{self.S} copies of the stream are not supported (1..{ops.HC_MAX_STREAMS})")
+        self.hc_prefixes = (hc.mixer_prefix, hc.ffn_prefix)
+        self.hc_optional = bool(hc.optional_tensors)
+        self.hidden_size = hidden_size
+        self.ctx = ctx
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not hasattr(norm, "gain_f32"):
+                raise ValueError(f"{type(norm).__name__} cannot stand before a sublayer of a hyper block (it has no gain_f32)")
+        self.hc = []   # per sublayer: (in [S], out [S], mix [S, S]) float32
+
+    def param_specs(self) -> List[ParamSpec]:
+        out = super().param_specs()
+        S = self.S
+        for prefix in self.hc_prefixes[:1 if self.ffn is None else 2]:
+            out += [ParamSpec(prefix + "in", (S,), role="bias", init="ones", optional=self.hc_optional),
+                    ParamSpec(prefix + "out", (S,), role="bias", init="ones", optional=self.hc_optional),
+                    ParamSpec(prefix + "mix", (S, S), role="bias", init="bias_normal", optional=self.hc_optional)]
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        super().bind(tensors)
+        S, dev = self.S, self.ctx.device
+        self.hc = []
+        for prefix in self.hc_prefixes[:1 if self.ffn is None else 2]:
+            def get(name, default):
+                t = tensors.get(prefix + name)
+                return (default.to(dev) if t is None else t.float()).contiguous()
+            self.hc.append((get("in", torch.ones(S)), get("out", torch.ones(S)), get("mix", torch.eye(S))))
+
+    takes_pending = False
+
+    def forward(self, residual, batch, cache, owns_cache: bool = True) -> None:
+        S = self.S
+        T = residual.shape[0]
+        write = batch.extras.pop("hc_write", None)     # the block before left its last write to this read
+        y_prev, mix_prev, out_prev = write if write is not None else (None, None, None)
+        w_in, w_out, w_mix = self.hc[0]
+        x = ops.hc_step(residual, S, y_prev, mix_prev, out_prev, in_w=w_in, gain=self.mixer_norm.gain_f32(),
+                        eps=self.mixer_norm.eps, out_dtype=self.ctx.dtype)
+        y = torch.empty((T, self.hidden_size), dtype=torch.float32, device=residual.device)
+        self.mixer.forward(x, y, batch, cache, owns_cache, accumulate=False)
+        if self.ffn is not None:
+            f_in, f_out, f_mix = self.hc[1]
+            x = ops.hc_step(residual, S, y, w_mix, w_out, in_w=f_in, gain=self.ffn_norm.gain_f32(), eps=self.ffn_norm.eps,
+                            out_dtype=self.ctx.dtype)
+            y = torch.empty((T, self.hidden_size), dtype=torch.float32, device=residual.device)
+            self.ffn.forward(x, y, batch, accumulate=False)
+            w_out, w_mix = f_out, f_mix
+        batch.extras["hc_write"] = (y, w_mix, w_out)
+
+
+def flush_hyper_write(residual, batch, streams: int) -> None:
+    """Makes the write that the last hyper block left open, so that ``residual`` holds the copies as they are."""
+    write = batch.extras.pop("hc_write", None)
+    if write is not None:
+        ops.hc_step(residual, streams, write[0], write[1], write[2])
+
+
+register_block("hyper", HyperBlock)

@@ -7,6 +7,11 @@ interleaved in blocks of 16 and the activation is computed in the epilogue of
 that matrix product, so gate and up never travel through memory; otherwise (the
 32-bit path, or sizes the tensor-core kernel refuses) the rows are gate then up
 and a separate kernel applies the activation.
+
+The spec may ask for another gated activation ("clamped_swish": g sigmoid(alpha g) (u + 1) on a gate clamped
+from above and an up projection clamped on both sides) and other tensor names; the gate/up product then has
+float32 results and one kernel applies the activation in float32.  :class:`DenseMLP` is the feed-forward
+without a gate, down(act(up x)), with act = max(z, 0)^2.
 """
 from __future__ import annotations
 
@@ -27,28 +32,70 @@ class SwiGLU(FeedForward):
         self.fused = False
         self.gate_up: Linear = None
         self.down: Linear = None
+        activation = getattr(spec, "activation", "silu")
+        if activation not in ops.GATED_ACTIVATIONS:
+            raise ValueError(f"unknown gated activation {activation!r}; known: {sorted(ops.GATED_ACTIVATIONS)}")
+        self.act = ops.GATED_ACTIVATIONS[activation]
+        self.limit, self.alpha = float(getattr(spec, "act_limit", 0.0)), float(getattr(spec, "act_alpha", 1.0))
+        self.gate_name, self.up_name, self.down_name = getattr(spec, "names", None) or (
+            "gate_proj.weight", "up_proj.weight", "down_proj.weight")
 
     def param_specs(self) -> List[ParamSpec]:
         I, H = self.intermediate_size, self.hidden_size
-        return [ParamSpec("gate_proj.weight", (I, H)), ParamSpec("up_proj.weight", (I, H)),
-                ParamSpec("down_proj.weight", (H, I))]
+        return [ParamSpec(self.gate_name, (I, H)), ParamSpec(self.up_name, (I, H)), ParamSpec(self.down_name, (H, I))]
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
-        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda and self.intermediate_size % ops.SWIGLU_BLOCK == 0
-                      and self.hidden_size % 8 == 0)
+        g, u = tensors[self.gate_name], tensors[self.up_name]
+        self.fused = (self.act == ops.ACT_SILU and g.dtype == torch.bfloat16 and g.is_cuda
+                      and self.intermediate_size % ops.SWIGLU_BLOCK == 0 and self.hidden_size % 8 == 0)
         if self.fused:
             self.gate_up = Linear(ops.interleave_gate_up(g, u))
         else:
             self.gate_up = Linear(torch.cat([g, u], dim=0))
-        self.down = Linear(tensors["down_proj.weight"])
+        self.down = Linear(tensors[self.down_name])
 
-    def forward(self, x, residual, batch) -> None:
+    def forward(self, x, residual, batch, accumulate: bool = True) -> None:
         if self.fused:
             a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True)
-        else:
+        elif self.act == ops.ACT_SILU:
             a = ops.swiglu(self.gate_up(x))
-        self.down.add_to(a, residual)
+        else:
+            a = ops.glu(self.gate_up(x, out_dtype=torch.float32), self.act, self.limit, self.alpha, out_dtype=x.dtype)
+        if accumulate:
+            self.down.add_to(a, residual)
+        else:
+            self.down(a, out=residual)
+
+
+class DenseMLP(FeedForward):
+    """``down(act(up x))`` without a gate; the activation runs in float32 on the up product's float32 result."""
+
+    def __init__(self, spec, hidden_size: int, ctx: BuildContext):
+        self.intermediate_size = int(spec.intermediate_size)
+        self.hidden_size = hidden_size
+        self.ctx = ctx
+        if spec.activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"unknown activation {spec.activation!r}; known: {sorted(ops.UNARY_ACTIVATIONS)}")
+        self.act = ops.UNARY_ACTIVATIONS[spec.activation]
+        self.up_name, self.down_name = spec.names
+        self.up: Linear = None
+        self.down: Linear = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        I, H = self.intermediate_size, self.hidden_size
+        return [ParamSpec(self.up_name, (I, H)), ParamSpec(self.down_name, (H, I))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.up = Linear(tensors[self.up_name])
+        self.down = Linear(tensors[self.down_name])
+
+    def forward(self, x, residual, batch, accumulate: bool = True) -> None:
+        a = ops.unary_act(self.up(x, out_dtype=torch.float32), self.act, out_dtype=x.dtype)
+        if accumulate:
+            self.down.add_to(a, residual)
+        else:
+            self.down(a, out=residual)
 
 
 register_ffn("swiglu", SwiGLU)
+register_ffn("dense_mlp", DenseMLP)

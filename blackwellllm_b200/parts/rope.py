@@ -10,8 +10,10 @@ host in float64 and stored as float32; the angle is the float32 product
 With ``interleaved`` the pair is (2j, 2j + 1); YaRN scaling (``rotary_inv_freq``,
 ``rotary_magnitude``) rescales the frequencies by how often a pair turns within the original context
 and multiplies cosines and sines by a constant.  ``norm_rotate_append`` is the general route: an
-optional RMS norm over the whole query and the whole key projection, then the rotation, for heads whose
-value size may differ from their key size.
+optional RMS norm over the whole query and the whole key projection (or, ``per_head``, over every head by
+itself with one gain vector shared by the heads), then the rotation, then an optional temperature on the
+queries that grows with the logarithm of the position (``q_temp``), for heads whose value size may differ
+from their key size; ``has_kv=False``: the rows hold queries only (a run that reads another run's cache).
 
 :class:`NoPosition` rotates nothing.  Both append rotated keys and raw values to
 the cache pages in the same kernel.
@@ -77,7 +79,12 @@ class RotaryEncoding(PositionEncoding):
             batch.extras[self._key] = table
         return table
 
-    def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True):
+    def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True,
+                           per_head=False, q_temp=None, has_kv=True):
+        if per_head or q_temp is not None or not has_kv:
+            return ops.head_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
+                                             self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
+                                             dq, dv, has_kv=has_kv, append=append, q_temp=q_temp)
         return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], self._table(batch), self.rotary_dim,
                                        self.interleaved, q_gain, k_gain, eps, cache.k_pages, cache.v_pages, nh, nkv,
                                        dq, dv, append=append)
@@ -139,7 +146,12 @@ class NoPosition(PositionEncoding):
         return ops.rope_append(qkv, batch.positions, batch.req_of_token, batch.block_tables[cache.group],
                                None, 0, cache.k_pages, cache.v_pages, nh, nkv, hd, append=append)
 
-    def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True):
+    def norm_rotate_append(self, qkv, batch, cache, nh, nkv, dq, dv, q_gain, k_gain, eps, append=True,
+                           per_head=False, q_temp=None, has_kv=True):
+        if per_head or q_temp is not None or not has_kv:
+            return ops.head_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
+                                             eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, has_kv=has_kv,
+                                             append=append, q_temp=q_temp)
         return ops.qk_norm_rope_append(qkv, batch, batch.block_tables[cache.group], None, 0, False, q_gain, k_gain,
                                        eps, cache.k_pages, cache.v_pages, nh, nkv, dq, dv, append=append)
 
