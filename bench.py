@@ -326,8 +326,40 @@ DESIGN_SHAPES = {
 }
 
 
+def _fuvevik_shape(width, heads, kv, hd, streams, dense_ff, experts, identity, top, ff, shared_ff, vocab, pairs):
+    """``pairs`` times (an attention layer with a dense feed-forward, an attention layer with a routed one); the second
+    pair on reads the keys and values of the first pair's layers; and the dense decoder of equal width, depth, heads
+    and about the ACTIVE feed-forward weights (two matrices of ``dense_ff`` = three of 2/3 of it; ``top`` experts and
+    the shared one)."""
+    def att(src=None):
+        m = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}
+        if src is not None:
+            m["kv_from"] = src
+        return m
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    layers = []
+    for p in range(pairs):
+        layers.append({"type": "attention", "mixer": att(None if p == 0 else 0), "mlp": {"kind": "dense", "ff": dense_ff}})
+        layers.append({"type": "attention", "mixer": att(None if p == 0 else 1), "mlp": moe})
+    design = {"architecture": "Fuvevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": streams, "layers": layers}
+    dense = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": width,
+             "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd,
+             "intermediate_size": (2 * dense_ff // 3 + top * ff + shared_ff) // 2 // 256 * 256,
+             "num_hidden_layers": 2 * pairs, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-6}
+    return design, dense
+
+
+FUVEVIK_SHAPES = {
+    # width, heads, kv heads, head size, copies of the stream, dense size, experts, identity outputs, top, expert size, shared size, vocab, pairs
+    "2k": (2048, 16, 4, 128, 4, 8192, 16, 2, 4, 1024, 1024, 32000, 2),
+    "4k": (4096, 32, 8, 128, 4, 14336, 8, 1, 2, 3584, 3584, 32000, 2),
+}
+DESIGNS = {"gafulix": (_gafulix_shape, DESIGN_SHAPES), "fuvevik": (_fuvevik_shape, FUVEVIK_SHAPES)}
+
+
 def design_comparison(args):
-    """Prefill and decode throughput of the Gafulix design beside the dense decoder of equal size (random
+    """Prefill and decode throughput of a design (``--design``) beside the dense decoder of equal size (random
     bfloat16 weights), and where each spends a step: time per launcher of one uncaptured prefill step and one
     uncaptured decode step, with what the design's own kernels reach of the measured peaks."""
     import torch
@@ -335,14 +367,15 @@ def design_comparison(args):
     from blackwellllm_b200.kernels import ops
     pk = peaks()
     T, B, C = args.prefill_tokens, args.batch, min(args.context, 2048)
-    out = {"workload": "design gafulix beside the dense decoder", "prefill_tokens": T, "decode_batch": B, "decode_context": C,
+    shape_of, shapes = DESIGNS[args.design]
+    out = {"workload": f"design {args.design} beside the dense decoder", "prefill_tokens": T, "decode_batch": B, "decode_context": C,
            "peaks": pk, "sizes": {}}
     gen = torch.Generator().manual_seed(7)
     for key in [k for k in args.design_sizes.split(",") if k]:
-        design, dense = _gafulix_shape(*DESIGN_SHAPES[key])
+        design, dense = shape_of(*shapes[key])
         V = design["vocab"]
         row = {}
-        for label, cfg in (("gafulix", design), ("dense", dense)):
+        for label, cfg in ((args.design, design), ("dense", dense)):
             page = 16
             eng = Engine.from_config(cfg, seed=3, std=0.02, dtype="bfloat16", page_size=page,
                                      num_pages=(B + 1) * -(-(max(T, C) + args.steps + args.warmup + 64) // page),
@@ -419,7 +452,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="run one part only (for profiling); the JSON line then lacks the other part")
-    ap.add_argument("--design", default=None, choices=["gafulix"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="instead of the default workload: this design beside the dense decoder of equal size")
     ap.add_argument("--design-sizes", default="2k,4k", help="which of the design comparison's sizes to run")
     args = ap.parse_args()

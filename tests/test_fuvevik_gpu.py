@@ -40,10 +40,10 @@ def test_embedding_with_position_vector(ops, H, copies, dtype):
     out = ops.embed_positions(table.to(DEV), ids.int().to(DEV), pos.int().to(DEV), sinusoid_frequencies(H, 10000.0).to(DEV),
                               copies=copies).cpu().view(9, copies, H)
     want = table[ids].double() + plain.position_vectors(pos, H, torch.float64)
+    # the angle is a float32 product of the position and a float32 frequency: its rounding grows with the position
+    bound = 2e-6 + pos.double() * 2.0 ** -22
     for c in range(copies):
-        # the angle is a float32 product: its rounding grows with the position (2^-24 relative)
-        assert float((out[:, c].double() - want).abs().max()) <= 2e-6 + 12345 * 2.0 ** -23
-    assert float((out[:5, 0].double() - want[:5]).abs().max()) <= 2e-6
+        assert torch.all((out[:, c].double() - want).abs().max(dim=1).values <= bound)
     plain_rows = ops.embed_positions(table.to(DEV), ids.int().to(DEV), pos.int().to(DEV), None, copies=1).cpu()
     assert torch.equal(plain_rows, table[ids].float())
 
@@ -240,12 +240,15 @@ def test_routed_ffn_float32(ops, E, identity, top, F, H, shared, T):
     want = plain.moe_ffn(x.double(), w, f)
     out = torch.full((T, H), 3.0, device=DEV)
     part.forward(x.to(DEV), out, None, accumulate=False)
+    ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
     assert float((out.cpu().double() - want).abs().max()) <= 2e-5 * float(want.abs().max())
     acc = torch.full((T, H), 3.0, device=DEV)
     part.forward(x.to(DEV), acc, None)
+    ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
     assert float((acc.cpu().double() - 3.0 - want).abs().max()) <= 2e-5 * float(want.abs().max())
     one = torch.zeros((1, H), device=DEV)
     part.forward(x[T // 2:T // 2 + 1].to(DEV), one, None, accumulate=False)
+    ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
     assert torch.equal(one[0], out[T // 2])
     # the correction decides the choice, not the weight: with a large one on the last output every token takes it first
     if identity:
@@ -255,6 +258,7 @@ def test_routed_ffn_float32(ops, E, identity, top, F, H, shared, T):
         w2["mlp.correction"] = w["mlp.correction"].clone()
         w2["mlp.correction"][-1] = 10.0
         part.forward(x.to(DEV), out, None, accumulate=False)
+        ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
         want2 = plain.moe_ffn(x.double(), w2, f)
         assert float((out.cpu().double() - want2).abs().max()) <= 2e-5 * float(want2.abs().max())
 
@@ -270,6 +274,7 @@ def test_routed_ffn_bfloat16_all_experts(ops, T):
     want = plain.moe_ffn(x.double(), w, f)
     out = torch.zeros((T, H), device=DEV)
     part.forward(x.to(DEV), out, None, accumulate=False)
+    ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
     assert float((out.cpu().double() - want).abs().max()) <= 2e-2 * float(want.abs().max())
     assert ops.moe_tc_status() == 0
 
@@ -287,11 +292,13 @@ def test_dense_feed_forwards(ops, dtype, H, F):
     part.bind({"up": up.to(DEV), "down": down.to(DEV)})
     out = torch.zeros((7, H), device=DEV)
     part.forward(x.to(DEV), out, None, accumulate=False)
+    ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
     want = plain.dense_ffn(x.double(), {"mlp.up": up.double(), "mlp.down": down.double()})
     assert float((out.cpu().double() - want).abs().max()) <= tol * float(want.abs().max())
     part = build_ffn(SwiGLUSpec(F, activation="clamped_swish", act_limit=0.7, act_alpha=1.702, names=("gate", "up", "down")), H, ctx)
     part.bind({"gate": gate.to(DEV), "up": up.to(DEV), "down": down.to(DEV)})
     part.forward(x.to(DEV), out, None)                     # added to what is there
+    ops.resolve_pending()      # a last product of few tokens leaves its sum to the next reader
     want = want + plain.clamped_expert(x.double(), gate.double(), up.double(), down.double(), 0.7)
     assert float((out.cpu().double() - want).abs().max()) <= tol * float(want.abs().max())
 
