@@ -46,6 +46,9 @@ struct Params {
     // sink != null: a row's softmax has one more term exp(sink[query head]) that has no key and no value
     // (its weight goes nowhere: the row's weights sum to less than one); float32 [nh], not scaled.
     const float* sink;
+    // gate != null: every output channel c < gate_dv of (token, head) is multiplied by sigmoid(gate[token * gate_ld +
+    // head * gate_dv + c]) as it is written, channels from gate_dv on become zero (bw::out_gate)
+    const float* gate; long long gate_ld; int gate_dv;
     // Decode rows straight from the q/k/v product (attn_keys_tma_kernel only; null: q holds the queries and
     // the cache this step's keys and values): qkv is float32 [planes][tokens][(nh + 2 nkv) * HD] to be added
     // up in plane order, the rotated channels of the q and k heads as (channel j, channel j + rd / 2) pairs;
@@ -322,11 +325,16 @@ attn_rows_kernel(Params p, int toks_per_tile) {
         const int tok = row / p.G, hg = row - tok * p.G;
         l += sink_term(p, g * p.G + hg, st.m[h]);
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok0 + tok) * p.nh + g * p.G + hg) * HD + 2 * (lane & 3);
+        const size_t token = (size_t)(p.cu_q[r] + tok0 + tok);
+        const int head = g * p.G + hg;
+        bf16* dst = p.out + (token * p.nh + head) * HD + 2 * (lane & 3);
 #pragma unroll
-        for (int j = 0; j < HD / 8; ++j)
+        for (int j = 0; j < HD / 8; ++j) {
+            const int c = j * 8 + 2 * (lane & 3);
             *reinterpret_cast<__nv_bfloat162*>(dst + j * 8) =
-                __floats2bfloat162_rn(o[j][2 * h] * inv, o[j][2 * h + 1] * inv);
+                __floats2bfloat162_rn(o[j][2 * h] * inv * bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, c),
+                                      o[j][2 * h + 1] * inv * bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, c + 1));
+        }
     }
 }
 
@@ -371,7 +379,8 @@ __device__ __forceinline__ void finish_keys(const Params& p, const RowState& st,
         if (n_slices == 1) {
             L += sink_term(p, g * p.G + hg, M);
             p.out[((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + c] =
-                __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+                __float2bfloat16_rn((L > 0.f ? acc / L : 0.f) *
+                                    bw::out_gate(p.gate, p.gate_ld, p.gate_dv, (size_t)(p.cu_q[r] + tok), g * p.G + hg, c));
         } else {
             // `item` counts the slices of all earlier items, so every (item, kv head, slice) has its own slot
             const size_t pr = ((size_t)item * p.nkv + (size_t)g * n_slices + slice) * 16 + row;
@@ -825,6 +834,14 @@ attn_merge_kernel(Params p, const int* merge_items) {
         L += sink_term(p, g * p.G + hg, M);
         const float inv = L > 0.f ? 1.f / L : 0.f;
         bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + tid * 4;
+        if (p.gate) {
+            const size_t token = (size_t)(p.cu_q[r] + tok);
+            const int head = g * p.G + hg;
+            acc.x *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, tid * 4);
+            acc.y *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, tid * 4 + 1);
+            acc.z *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, tid * 4 + 2);
+            acc.w *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, tid * 4 + 3);
+        }
         const uint2 packed = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
         *reinterpret_cast<uint2*>(dst) = packed;
     }
@@ -871,6 +888,14 @@ attn_merge_few_kernel(Params p, const int* merge_items) {
     L += sink_term(p, g * p.G + hg, M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     bf16* dst = p.out + ((size_t)(p.cu_q[r] + tok) * p.nh + g * p.G + hg) * HD + quad * 4;
+    if (p.gate) {
+        const size_t token = (size_t)(p.cu_q[r] + tok);
+        const int head = g * p.G + hg;
+        acc.x *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, quad * 4);
+        acc.y *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, quad * 4 + 1);
+        acc.z *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, quad * 4 + 2);
+        acc.w *= bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, head, quad * 4 + 3);
+    }
     *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
 }
 
@@ -892,7 +917,7 @@ BW_EXPORT int bw_attention_head_dim() { return HD; }
 // the q/k/v product itself: float32 [qkv_planes][tokens][(nh + 2 nkv) * HD], the planes qkv_plane_stride
 // floats apart and added in order, the rotated channels of the q and k heads as (j, j + rd / 2) pairs;
 // rope_table float32 [tokens][rd] (cosines, then sines); append != 0: key and value also go to the cache.
-// sink: float32 [nh] or null (see Params).
+// sink: float32 [nh] or null; gate: float32 [tokens, >= nh * gate_dv] with rows gate_ld apart, or null (see Params).
 // Only where the TMA key-slice kernel runs (head size a multiple of 64, pages of 8 to 64 tokens);
 // BW_ERR_UNSUPPORTED otherwise, and nothing was launched.
 BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
@@ -901,7 +926,8 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
                                const int* merge_work, int n_merge_items, float* part_o, float* part_ml, int nh,
                                int nkv, int page_size, int num_pages, int window, int chunk, float scale,
                                const float* qkv, int qkv_planes, long long qkv_plane_stride, const float* rope_table,
-                               int rd, int append, int merge_max_slices, const float* sink, void* stream) {
+                               int rd, int append, int merge_max_slices, const float* sink, const float* gate, long long gate_ld,
+                               int gate_dv, void* stream) {
     if (nkv <= 0 || nh % nkv != 0) return BW_ERR_BAD_ARG;
     const int G = nh / nkv;
     if (G > 16) return BW_ERR_UNSUPPORTED;
@@ -925,6 +951,8 @@ BW_EXPORT int bw_attention_mma(const void* q, const void* k_pages, const void* v
     p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sink = sink;
+    if (gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
+    p.gate = gate; p.gate_ld = gate_ld; p.gate_dv = gate_dv;
     p.qkv = qkv; p.qkv_plane_stride = qkv_plane_stride; p.rope_table = rope_table;
     p.qkv_planes = qkv_planes; p.rd = rd; p.append = append;
     if (n_rows_items > 0) {

@@ -22,7 +22,8 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
                       const KT* __restrict__ v_pages, const int* __restrict__ positions,
                       const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                       int max_blocks, OT* __restrict__ out, int nh, int nkv, int hd, int page_size,
-                      int num_pages, int window, int chunk, float scale, const float* __restrict__ sink) {
+                      int num_pages, int window, int chunk, float scale, const float* __restrict__ sink,
+                      const float* __restrict__ gate, long long gate_ld, int gate_dv) {
     extern __shared__ float smem[];
     float* qs = smem;                       // [hd]
     float* accs = qs + hd;                  // [WARPS][hd]
@@ -102,18 +103,21 @@ attention_simt_kernel(const QT* __restrict__ q, const KT* __restrict__ k_pages,
     for (int c = threadIdx.x; c < hd; c += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < WARPS; ++w) o += accs[w * hd + c] * f[w];
-        out[((size_t)t * nh + h) * hd + c] = bw::from_f32<OT>(o * inv);
+        out[((size_t)t * nh + h) * hd + c] = bw::from_f32<OT>(o * inv * bw::out_gate(gate, gate_ld, gate_dv, (size_t)t, h, c));
     }
 }
 
 }  // namespace
 
 // sink: float32 [nh] or null: exp(sink[head]) joins every row's softmax denominator (unscaled, no key, no value).
+// gate: float32 [T, >= nh * gate_dv], rows gate_ld apart, or null: output channel c < gate_dv of (token, head) is
+// multiplied by sigmoid(gate[token, head * gate_dv + c]); channels from gate_dv on become zero.
 // type: element type of q, the pages and out (all the same).  window <= 0: no window; chunk <= 0: no blocks (bw::first_visible).
 BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* v_pages, int type,
                                 const int* positions, const int* req_of_token, const int* block_table,
                                 int max_blocks, void* out, int T, int nh, int nkv, int hd, int page_size,
-                                int num_pages, int window, int chunk, float scale, const float* sink, void* stream) {
+                                int num_pages, int window, int chunk, float scale, const float* sink, const float* gate,
+                                long long gate_ld, int gate_dv, void* stream) {
     if (T <= 0) return 0;
     if (hd <= 0 || hd > 32 * MAX_CH || nkv <= 0 || nh % nkv != 0) return BW_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -122,11 +126,11 @@ BW_EXPORT int bw_attention_simt(const void* q, const void* k_pages, const void* 
     if (type == BW_F32)
         attention_simt_kernel<float, float, float><<<grid, WARPS * 32, smem, s>>>(
             (const float*)q, (const float*)k_pages, (const float*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink);
+            block_table, max_blocks, (float*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv);
     else if (type == BW_BF16)
         attention_simt_kernel<bf16, bf16, bf16><<<grid, WARPS * 32, smem, s>>>(
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, positions, req_of_token,
-            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink);
+            block_table, max_blocks, (bf16*)out, nh, nkv, hd, page_size, num_pages, window, chunk, scale, sink, gate, gate_ld, gate_dv);
     else return BW_ERR_BAD_ARG;
     BW_LAUNCH_CHECK();
     return 0;

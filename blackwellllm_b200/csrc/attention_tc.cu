@@ -57,6 +57,9 @@ struct Params {
     int max_blocks, nh, nkv, G, page_size, window, chunk, tpt;
     float scale_log2;
     const float* sink;   // float32 [nh] or null: exp(sink[query head]) joins the row's softmax denominator (no key, no value, not scaled)
+    // gate != null: output channel c < gate_dv of (token, head) times sigmoid(gate[token * gate_ld + head * gate_dv + c]),
+    // channels from gate_dv on zero (bw::out_gate)
+    const float* gate; long long gate_ld; int gate_dv;
 };
 
 // 2^x, one MUFU instruction (the flush of denormal results to zero does not matter for softmax weights)
@@ -324,6 +327,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bw::tmem_ld_32x32(tmem_O + lane_base + c0, v);
                 bw::tmem_ld_wait();
                 if (row_ok) {
+                    if (p.gate) {
+                        const size_t token = (size_t)(p.cu_q[r] + tok0 + tok);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            v[c] = __float_as_uint(__uint_as_float(v[c]) * bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, g * p.G + hg, c0 + c));
+                    }
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         *reinterpret_cast<uint4*>(dst + c0 + c) =
@@ -385,7 +394,8 @@ BW_EXPORT int bw_attention_tc_supported(int nh, int nkv, int page_size) {
 BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_q,
                               const int* q_start, const int* kv_len, const int* block_table, int max_blocks,
                               const int* work, int n_items, int T, int nh, int nkv, int page_size, int num_pages,
-                              int window, int chunk, float scale, const float* sink, void* stream) {
+                              int window, int chunk, float scale, const float* sink, const float* gate, long long gate_ld,
+                              int gate_dv, void* stream) {
     if (n_items <= 0) return 0;
     if (!bw_attention_tc_supported(nh, nkv, page_size) || !(scale > 0.f)) return BW_ERR_UNSUPPORTED;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages | (uintptr_t)out) & 15) != 0) return BW_ERR_UNSUPPORTED;
@@ -411,6 +421,8 @@ BW_EXPORT int bw_attention_tc(const void* q, const void* k_pages, const void* v_
     p.window = window > 0 ? window : 0; p.chunk = chunk > 0 ? chunk : 0; p.tpt = tpt;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.sink = sink;
+    if (gate && (gate_dv <= 0 || gate_dv > HD || gate_ld < (long long)nh * gate_dv)) return BW_ERR_BAD_ARG;
+    p.gate = gate; p.gate_ld = gate_ld; p.gate_dv = gate_dv;
     bw::launch((attn_tc_kernel), dim3((unsigned)n_items * nkv), dim3(THREADS), SMEM_BYTES, (cudaStream_t)stream, tq, tk, tv, p);
     BW_LAUNCH_CHECK();
     return 0;

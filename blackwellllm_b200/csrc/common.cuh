@@ -144,6 +144,14 @@ __device__ __forceinline__ float unary_act(int act, float x) {
     return x;
 }
 
+// The output gate of an attention mixer: sigmoid(gate[token, head * dv + c]) for c < dv, 0 for the pad channels beyond
+// dv, 1 without a gate.  gate: float32 rows `ld` apart.
+__device__ __forceinline__ float out_gate(const float* __restrict__ gate, long long ld, int dv, size_t token, int head, int c) {
+    if (!gate) return 1.f;
+    if (c >= dv) return 0.f;
+    return 1.f / (1.f + expf(-gate[token * (size_t)ld + (size_t)head * dv + c]));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

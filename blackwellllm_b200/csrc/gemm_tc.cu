@@ -76,8 +76,24 @@ struct Epilogue {
     int tma_add;          // normal orientation, out += : 32 x 32 boxes go out through the tensor map tmC
     int stream;           // the k-blocks of all tiles, laid end to end, are cut into one equal range per CTA
     int planes;           // split-K: the partial planes ARE the result (the bias in plane 0); whoever reads them adds them up
+    // an activation of common.cuh on the finished sums.  With swiglu: the gated one that replaces silu(g) * u
+    // (BW_ACT_SILU, BW_ACT_CLAMPED_SWISH with its limit and alpha); without: 0 = none, BW_ACT_RELU2 on every value.
+    int act; float act_limit, act_alpha;
     RopeOut rope;
 };
+
+__device__ __forceinline__ float ep_glu(const Epilogue& ep, float g, float u) {
+    if (ep.act == BW_ACT_CLAMPED_SWISH) {
+        g = fminf(g, ep.act_limit);
+        u = fminf(fmaxf(u, -ep.act_limit), ep.act_limit) + 1.f;
+        return __fdividef(g, 1.f + __expf(-ep.act_alpha * g)) * u;
+    }
+    return __fdividef(g, 1.f + __expf(-g)) * u;
+}
+__device__ __forceinline__ float ep_unary(const Epilogue& ep, float v) {
+    if (ep.act == BW_ACT_RELU2) { v = fmaxf(v, 0.f); return v * v; }
+    return v;
+}
 
 __device__ __forceinline__ float bias_at(const Epilogue& ep, int feature) {
     if (!ep.bias) return 0.f;
@@ -199,7 +215,7 @@ __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const floa
             const float other = __shfl_xor_sync(0xffffffffu, vals[c], 16);
             if (c < nvalid && fvalid && lane < SWIGLU_BLOCK)
                 ((bf16*)ep.out)[(size_t)(token0 + c) * ep.ldo + j] =
-                    __float2bfloat16_rn(__fdividef(vals[c], 1.f + __expf(-vals[c])) * other);
+                    __float2bfloat16_rn(ep_glu(ep, vals[c], other));
         }
         return;
     }
@@ -226,12 +242,12 @@ __device__ __forceinline__ void emit(const Epilogue& ep, float* part, const floa
         }
 #pragma unroll
         for (int c = 0; c < N; ++c)
-            if (c < nvalid) o[(size_t)c * ep.ldo] = vals[c] + b + (ep.accumulate ? old[c] : 0.f);
+            if (c < nvalid) o[(size_t)c * ep.ldo] = ep_unary(ep, vals[c] + b) + (ep.accumulate ? old[c] : 0.f);
     } else {
         bf16* o = (bf16*)ep.out + off;
 #pragma unroll
         for (int c = 0; c < N; ++c)
-            if (c < nvalid) o[(size_t)c * ep.ldo] = __float2bfloat16_rn(vals[c] + b);
+            if (c < nvalid) o[(size_t)c * ep.ldo] = __float2bfloat16_rn(ep_unary(ep, vals[c] + b));
     }
 }
 
@@ -311,7 +327,7 @@ __device__ __forceinline__ void swiglu_direct(const Epilogue& ep, const uint32_t
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const float g = __uint_as_float(v[i]), u = __uint_as_float(v[16 + i]);
-        y[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+        y[i] = ep_glu(ep, g, u);
     }
     bf16* dst = (bf16*)ep.out + (size_t)token * ep.ldo + (f0 / (2 * SWIGLU_BLOCK)) * SWIGLU_BLOCK;
     if ((ep.ldo & 7) == 0 && ((uintptr_t)ep.out & 15) == 0) {
@@ -892,6 +908,7 @@ __global__ void splitk_reduce_kernel(Epilogue ep) {
                 v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
             }
             if (ep.bias) { v.x += bias_at(ep, j); v.y += bias_at(ep, j + 1); v.z += bias_at(ep, j + 2); v.w += bias_at(ep, j + 3); }
+            v.x = ep_unary(ep, v.x); v.y = ep_unary(ep, v.y); v.z = ep_unary(ep, v.z); v.w = ep_unary(ep, v.w);
             float4* o = reinterpret_cast<float4*>((float*)ep.out + (size_t)token * ep.ldo + j);
             if (ep.accumulate) { const float4 old = *o; v.x = old.x + v.x; v.y = old.y + v.y; v.z = old.z + v.z; v.w = old.w + v.w; }
             *o = v;
@@ -907,7 +924,7 @@ __global__ void splitk_reduce_kernel(Epilogue ep) {
                 g += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fg];
                 u += ep.partial[(size_t)s * plane + (size_t)token * ep.features + fu];
             }
-            ((bf16*)ep.out)[(size_t)token * ep.ldo + j] = __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+            ((bf16*)ep.out)[(size_t)token * ep.ldo + j] = __float2bfloat16_rn(ep_glu(ep, g, u));
             continue;
         }
         if (ep.rope_on) {
@@ -925,6 +942,7 @@ __global__ void splitk_reduce_kernel(Epilogue ep) {
         float v = 0.f;
         for (int s = 0; s < ep.splits; ++s) v += ep.partial[(size_t)s * plane + i];
         if (ep.bias) v += ep.bias_type == BW_F32 ? ((const float*)ep.bias)[j] : __bfloat162float(((const bf16*)ep.bias)[j]);
+        v = ep_unary(ep, v);
         const size_t off = (size_t)token * ep.ldo + j;
         if (ep.out_type == BW_F32) {
             float* o = (float*)ep.out + off;
@@ -1118,8 +1136,12 @@ constexpr int PLANES_MAX_TOKENS = 256;   // bw_gemm_tc_planes: the orientation w
 static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
                        int M, int N, int K, long long ldx, long long ldo, int accumulate, int swiglu,
                        float* workspace, long long workspace_elems, int* counters, long long n_counters,
-                       int force_splits, const RopeOut* rope, void* stream, int* planes_out = nullptr) {
+                       int force_splits, const RopeOut* rope, void* stream, int* planes_out = nullptr,
+                       int act = 0, float act_limit = 0.f, float act_alpha = 1.f) {
     if (M <= 0 || N <= 0) return 0;
+    // act: with swiglu the gated activation (BW_ACT_SILU or BW_ACT_CLAMPED_SWISH); without, 0 or BW_ACT_RELU2 on the sums
+    if (swiglu ? (act != BW_ACT_SILU && act != BW_ACT_CLAMPED_SWISH) : (act != 0 && act != BW_ACT_RELU2)) return BW_ERR_BAD_ARG;
+    if (!swiglu && act != 0 && (accumulate || rope || planes_out)) return BW_ERR_BAD_ARG;
     // planes_out: the product is left as *planes_out float32 planes [M, N] in `out` (row stride N, the bias
     // in the first), to be added up by its reader; K is split as if the sums were made here.
     const bool planes = planes_out != nullptr;
@@ -1187,6 +1209,7 @@ static int run_gemm_tc(const void* x, const void* w, const void* bias, int bias_
     if (planes) *planes_out = splits;
     ep.bias = bias; ep.ldo = ldo;
     ep.out_type = out_type; ep.bias_type = bias_type; ep.accumulate = accumulate; ep.transposed = tr;
+    ep.act = act; ep.act_limit = act_limit; ep.act_alpha = act_alpha;
     ep.swiglu = swiglu; ep.tokens = M; ep.features = N; ep.splits = splits;
     ep.rope_on = rope ? 1 : 0;
     ep.stream = stream_k ? 1 : 0;
@@ -1238,6 +1261,17 @@ BW_EXPORT int bw_gemm_tc(const void* x, const void* w, const void* bias, int bia
                          int force_splits, void* stream) {
     return run_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, ldx, ldo, accumulate, swiglu, workspace,
                        workspace_elems, counters, n_counters, force_splits, nullptr, stream);
+}
+
+// bw_gemm_tc with an activation on the finished sums: with swiglu the gated activation `act` in place of
+// silu(gate) * up (BW_ACT_CLAMPED_SWISH: g sigmoid(alpha g) (u + 1) on the clamped gate and up); without swiglu
+// BW_ACT_RELU2 on every value of a result that is written (not added).
+BW_EXPORT int bw_gemm_tc_act(const void* x, const void* w, const void* bias, int bias_type, void* out, int out_type,
+                             int M, int N, int K, long long ldx, long long ldo, int swiglu, int act, float act_limit,
+                             float act_alpha, float* workspace, long long workspace_elems, int* counters,
+                             long long n_counters, int force_splits, void* stream) {
+    return run_gemm_tc(x, w, bias, bias_type, out, out_type, M, N, K, ldx, ldo, 0, swiglu, workspace,
+                       workspace_elems, counters, n_counters, force_splits, nullptr, stream, nullptr, act, act_limit, act_alpha);
 }
 
 // The product of up to 256 tokens as float32 planes: planes[p][m][n] for p < *n_planes add up to

@@ -21,6 +21,76 @@ namespace {
 
 constexpr int MAX_STREAMS = 8;
 
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(bw::pack_bf16x2(a, b), bw::pack_bf16x2(c, d));
+}
+
+// The same with four channels a thread and 16-byte accesses (H a multiple of 4, every pointer 16-byte aligned).
+template <typename OT, int S>
+__global__ void __launch_bounds__(256)
+hc_step_vec4_kernel(float* __restrict__ streams, const float* __restrict__ y, const float* __restrict__ mix,
+                    const float* __restrict__ out_w, const float* __restrict__ in_w, const float* __restrict__ gain,
+                    const int* __restrict__ rows, OT* __restrict__ out, int H, float eps, int write_back) {
+    BW_PDL_TRIGGER();
+    extern __shared__ __align__(16) float urow[];
+    __shared__ float scratch[32];
+    __shared__ float s_mix[S * S], s_out[S], s_in[S];
+    if (threadIdx.x < S * S) s_mix[threadIdx.x] = y ? mix[threadIdx.x] : ((threadIdx.x / S == threadIdx.x % S) ? 1.f : 0.f);
+    if (threadIdx.x < S) { s_out[threadIdx.x] = y ? out_w[threadIdx.x] : 0.f; s_in[threadIdx.x] = in_w ? in_w[threadIdx.x] : 0.f; }
+    __syncthreads();
+    BW_PDL_WAIT();
+    const int t = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xs = streams + (size_t)t * S * H;
+    const float* yr = y ? y + (size_t)t * H : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {
+        float4 old[S], now[S];
+#pragma unroll
+        for (int s = 0; s < S; ++s) old[s] = *reinterpret_cast<const float4*>(xs + (size_t)s * H + c);
+        if (yr) {
+            const float4 yv = *reinterpret_cast<const float4*>(yr + c);
+#pragma unroll
+            for (int r = 0; r < S; ++r) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+                    const float m = s_mix[s * S + r];
+                    a.x = fmaf(m, old[s].x, a.x); a.y = fmaf(m, old[s].y, a.y); a.z = fmaf(m, old[s].z, a.z); a.w = fmaf(m, old[s].w, a.w);
+                }
+                const float o = s_out[r];
+                now[r] = make_float4(fmaf(o, yv.x, a.x), fmaf(o, yv.y, a.y), fmaf(o, yv.z, a.z), fmaf(o, yv.w, a.w));
+            }
+            if (write_back) {
+#pragma unroll
+                for (int r = 0; r < S; ++r) *reinterpret_cast<float4*>(xs + (size_t)r * H + c) = now[r];
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < S; ++r) now[r] = old[r];
+        }
+        if (in_w) {
+            float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                const float w = s_in[s];
+                u.x = fmaf(w, now[s].x, u.x); u.y = fmaf(w, now[s].y, u.y); u.z = fmaf(w, now[s].z, u.z); u.w = fmaf(w, now[s].w, u.w);
+            }
+            *reinterpret_cast<float4*>(urow + c) = u;
+            ss = fmaf(u.x, u.x, ss); ss = fmaf(u.y, u.y, ss); ss = fmaf(u.z, u.z, ss); ss = fmaf(u.w, u.w, ss);
+        }
+    }
+    if (!in_w) return;
+    OT* o = out + (size_t)blockIdx.x * H;
+    float r = 1.f;
+    if (gain) r = rsqrtf(bw::block_sum(ss, scratch) / (float)H + eps);
+    for (int c = threadIdx.x * 4; c < H; c += blockDim.x * 4) {   // each thread reads back what it wrote
+        const float4 u = *reinterpret_cast<const float4*>(urow + c);
+        const float4 g = gain ? *reinterpret_cast<const float4*>(gain + c) : make_float4(1.f, 1.f, 1.f, 1.f);
+        store4(o + c, u.x * r * g.x, u.y * r * g.y, u.z * r * g.z, u.w * r * g.w);
+    }
+}
+
 template <typename OT, int S>
 __global__ void __launch_bounds__(256)
 hc_step_kernel(float* __restrict__ streams, const float* __restrict__ y, const float* __restrict__ mix,
@@ -81,8 +151,17 @@ hc_step_kernel(float* __restrict__ streams, const float* __restrict__ y, const f
 template <typename OT, int S>
 int launch_hc(float* streams, const float* y, const float* mix, const float* out_w, const float* in_w, const float* gain,
               const int* rows, void* out, int n, int H, float eps, int write_back, cudaStream_t s) {
-    static bool raised[bw::MAX_DEVICES] = {};
+    static bool raised[bw::MAX_DEVICES] = {}, raised4[bw::MAX_DEVICES] = {};
     const size_t smem = (size_t)H * sizeof(float);
+    const bool vec = (H & 3) == 0 && (((uintptr_t)streams | (uintptr_t)y | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
+    if (vec) {
+        if (smem > 48 * 1024 && bw::allow_dynamic_smem(hc_step_vec4_kernel<OT, S>, 200 * 1024, raised4) != cudaSuccess) return BW_ERR_DRIVER;
+        const int threads = H >= 1024 ? 256 : 128;
+        bw::launch((hc_step_vec4_kernel<OT, S>), dim3(n), dim3(threads), smem, s, streams, y, mix, out_w, in_w, gain, rows, (OT*)out, H, eps,
+                   write_back);
+        BW_LAUNCH_CHECK();
+        return 0;
+    }
     if (smem > 48 * 1024 && bw::allow_dynamic_smem(hc_step_kernel<OT, S>, 200 * 1024, raised) != cudaSuccess) return BW_ERR_DRIVER;
     bw::launch((hc_step_kernel<OT, S>), dim3(n), dim3(256), smem, s, streams, y, mix, out_w, in_w, gain, rows, (OT*)out, H, eps, write_back);
     BW_LAUNCH_CHECK();

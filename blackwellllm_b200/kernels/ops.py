@@ -457,9 +457,10 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, positions: torch.Tensor,
                    req_of_token: torch.Tensor, block_table: torch.Tensor, nh: int, window: Optional[int],
                    scale: float, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                   sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None) -> torch.Tensor:
     _dev(q, "q"); _dev(k_pages, "k_pages", q.dtype); _dev(v_pages, "v_pages", q.dtype)
     _check_sink(sink, nh)
+    g, g_ld, g_dv = _gate_args(gate, q.shape[0], nh, k_pages.shape[3])
     _dev(positions, "positions", torch.int32); _dev(req_of_token, "req_of_token", torch.int32)
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
@@ -470,11 +471,23 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
         out = torch.empty_like(q)
     fn = _fn("attention_simt", "bw_attention_simt",
              [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_ll, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q, "q"), _ptr(positions), _ptr(req_of_token),
               _ptr(block_table), block_table.shape[1], _ptr(out), T, nh, nkv, hd, page_size, num_pages,
-              int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _stream()), "attention_simt")
+              int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv, _stream()), "attention_simt")
     return out
+
+
+def _gate_args(gate: Optional[tuple], T: int, nh: int, hd: int):
+    """``gate`` = (float32 tensor [T, nh * dv], possibly a column range of a wider one; dv): what the attention
+    kernels take as pointer, row stride and value size."""
+    if gate is None:
+        return None, 0, 0
+    g, dv = gate
+    _dev(g, "gate", torch.float32, contiguous=False)
+    if g.shape != (T, nh * dv) or g.stride(1) != 1 or not 0 < dv <= hd:
+        raise KernelError(f"attention: the gate must be float32 [T, nh * dv] with contiguous rows and dv <= {hd}")
+    return g, g.stride(0), int(dv)
 
 
 def _check_sink(sink: Optional[torch.Tensor], nh: int) -> None:
@@ -545,6 +558,8 @@ def log_prob(logits: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
 
 _GEMM_TC_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,
                  c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p]
+_GEMM_TC_ACT_ARGS = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_int, c_int,
+                     c_float, c_float, c_void_p, c_ll, c_void_p, c_ll, c_int, c_void_p]
 _WORKSPACE_BYTES = 64 << 20
 _COUNTERS = 1 << 16
 _workspaces = {}
@@ -604,10 +619,13 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
             out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-            accumulate: bool = False, force_splits: int = 0, swiglu: bool = False) -> torch.Tensor:
+            accumulate: bool = False, force_splits: int = 0, swiglu: bool = False,
+            act: Optional[int] = None, limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """out (=|+=) x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, float32 sums).
     ``swiglu``: ``w`` is a gate/up weight from :func:`interleave_gate_up`; the result is
-    bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue."""
+    bfloat16 [M, N / 2] = silu(gate) * up, computed in the epilogue; ``act`` = ACT_CLAMPED_SWISH (with its
+    ``limit`` and ``alpha``) puts that gated activation in its place (:func:`glu`).  Without ``swiglu``,
+    ``act`` = ACT_RELU2 squares the positive part of every sum of a result that is written (not added)."""
     _dev(x, "x", torch.bfloat16, contiguous=False); _dev(w, "w", torch.bfloat16)
     if not gemm_tc_supports(x, w):
         raise KernelError("gemm_tc: operands must be bfloat16 with K and the row stride multiples of 8 "
@@ -633,6 +651,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         if bias.numel() != N:
             raise KernelError("gemm: bias must have N entries")
     ws, counters = _workspace(x.device)
+    if act is not None and not (swiglu and act == ACT_SILU):
+        if accumulate:
+            raise KernelError("gemm_tc: an activation goes with a result that is written, not added")
+        fn = _fn("gemm_tc", "bw_gemm_tc_act", _GEMM_TC_ACT_ARGS, macros=_gemm_macros(),
+                 tag=f"act{M}x{N}x{K}" if _timings is not None else None)
+        _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(out),
+                  _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(swiglu), int(act), float(limit), float(alpha),
+                  _ptr(ws), ws.numel(), _ptr(counters), counters.numel(), int(force_splits), _stream()), "gemm_tc_act")
+        return out
     fn = _fn("gemm_tc", "bw_gemm_tc", _GEMM_TC_ARGS, macros=_gemm_macros(), tag=f"{M}x{N}x{K}" if _timings is not None else None)
     _check(fn(_ptr(x), _ptr(w), _ptr(bias), _code(bias, "bias") if bias is not None else 0, _ptr(out),
               _code(out, "out"), M, N, K, x.stride(0), out.stride(0), int(accumulate), int(swiglu), _ptr(ws),
@@ -747,26 +774,29 @@ def attention_takes_unrotated(hd: int, page_size: int) -> bool:
 
 def paged_attention(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch,
                     block_table: torch.Tensor, nh: int, window: Optional[int], scale: float,
-                    chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    chunk: Optional[int] = None, sink: Optional[torch.Tensor] = None,
+                    gate: Optional[tuple] = None) -> torch.Tensor:
     """Causal attention of the batch's tokens over the paged cache (which already
     holds this step's keys and values, unless ``q`` is an :class:`UnrotatedQKV`).  float32: the
     CUDA-core kernel; bfloat16: the tensor-core kernel built for this head size.  A query sees the keys
     from ``first_visible(position, window, chunk)`` on: the latest ``window`` keys, and none before the
     start of its own block of ``chunk`` positions (blocks are counted from position 0).  ``sink`` (float32, one
-    entry per query head): the softmax of a row has one more term exp(sink) that has no key and no value."""
+    entry per query head): the softmax of a row has one more term exp(sink) that has no key and no value.
+    ``gate`` = (g float32 [T, nh * dv], dv): channel c < dv of every head's output is multiplied by
+    sigmoid(g[t, head * dv + c]) as it is written; channels from dv on (padding) become zero."""
     if isinstance(q, UnrotatedQKV):
         if batch.T == batch.R and attention_takes_unrotated(k_pages.shape[3], k_pages.shape[2]):
-            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink)
+            return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate)
         q = q.materialise()
     if q.dtype == torch.float32:
         return attention_simt(q, k_pages, v_pages, batch.positions, batch.req_of_token, block_table, nh,
-                              window, scale, chunk=chunk, sink=sink)
-    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink)
+                              window, scale, chunk=chunk, sink=sink, gate=gate)
+    return attention_mma(q, k_pages, v_pages, batch, block_table, nh, window, scale, chunk, sink, gate)
 
 
 _ATTN_MMA_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                    c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+                                   c_void_p, c_int, c_ll, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p]
 
 
 _sm_counts = {}
@@ -855,9 +885,10 @@ def attention_work(batch, G: int, nkv: int, window: Optional[int], hd: int = 128
 
 def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_table: torch.Tensor,
                   nh: int, window: Optional[int], scale: float, chunk: Optional[int] = None,
-                  sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  sink: Optional[torch.Tensor] = None, gate: Optional[tuple] = None) -> torch.Tensor:
     _dev(k_pages, "k_pages", torch.bfloat16); _dev(v_pages, "v_pages", torch.bfloat16)
     _check_sink(sink, nh)
+    g, g_ld, g_dv = _gate_args(gate, batch.T, nh, k_pages.shape[3])
     _dev(block_table, "block_table", torch.int32)
     num_pages, nkv, page_size, hd = k_pages.shape
     raw = q if isinstance(q, UnrotatedQKV) else None
@@ -896,7 +927,7 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
         tc = _fn("attention_tc", "bw_attention_tc", _ATTN_TC_ARGS, macros=attention_tc_macros(hd))
         _check(tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(batch.cu_q), _ptr(batch.q_start),
                   _ptr(batch.kv_len), _ptr(block_table), block_table.shape[1], _ptr(rows_w), n_rows, q.shape[0],
-                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _stream()), "attention_tc")
+                  nh, nkv, page_size, num_pages, int(window or 0), int(chunk or 0), float(scale), _ptr(sink), _ptr(g), g_ld, g_dv, _stream()), "attention_tc")
         n_rows = 0
         if not n_keys:
             return out
@@ -908,11 +939,12 @@ def attention_mma(q, k_pages: torch.Tensor, v_pages: torch.Tensor, batch, block_
               _ptr(raw.planes if raw is not None else None), raw.planes.shape[0] if raw is not None else 0,
               raw.planes.stride(0) if raw is not None else 0, _ptr(raw.table if raw is not None else None),
               raw.rotary_dim if raw is not None else 0, int(raw.append) if raw is not None else 0, merge_max,
-              _ptr(sink), _stream()), "attention_mma")
+              _ptr(sink), _ptr(g), g_ld, g_dv, _stream()), "attention_mma")
     return out
 
 
-_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p]
+_ATTN_TC_ARGS = [c_void_p] * 8 + [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                  c_void_p, c_ll, c_int, c_void_p]
 
 
 def attention_tc_supports(hd: int, G: int, page_size: int) -> bool:

@@ -22,7 +22,8 @@ Further options, each of which takes that route too: ``qk_norm = "head"`` (every
 itself, one gain vector of the head's size shared by the heads), ``q_temperature`` (the queries of position p
 times 1 + coef ln(floor((p + 1) / every) + 1)), ``sink`` (one learned number per query head whose exponential
 joins the softmax's denominator: the kernels add it when they normalise a row), ``output_gate`` (the heads'
-outputs times sigmoid(W_g x) before the output projection; W_g's rows ride in the q/k/v product), and
+outputs times sigmoid(W_g x) before the output projection; W_g's rows ride in the q/k/v product and the
+attention kernels apply the sigmoid as they write a row), and
 ``shares_kv`` (no key and value tensors: the run reads the cache of the schedule entry it names, which the
 other layer filled earlier in the same step, with its own queries).
 """
@@ -159,12 +160,13 @@ class GQAAttention(Mixer):
                                                      self.k_gain, float(self.qk_norm_eps or 0.0), append=owns_cache)
             else:
                 q = self.position.rotate_append(qkv, batch, cache, self.nh, self.nkv, self.hd, append=owns_cache)
-        o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
-                                self.nh, self.window, self.scale, self.chunk, self.sink)
-        if self.gated:
+        gate = None
+        if self.gated:   # the attention kernels multiply by the gate's sigmoid as they write a row
             g = self.gate(x, out_dtype=torch.float32) if self.gate is not None \
                 else qkv[:, self.g_off:self.g_off + self.nh * self.dv]
-            ops.sigmoid_gate(o, g, self.nh, self.dv)
+            gate = (g, self.dv)
+        o = ops.paged_attention(q, cache.k_pages, cache.v_pages, batch, batch.block_tables[cache.group],
+                                self.nh, self.window, self.scale, self.chunk, self.sink, gate)
         if accumulate:
             self.o.add_to(o, residual)
         else:

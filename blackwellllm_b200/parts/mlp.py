@@ -9,7 +9,7 @@ that matrix product, so gate and up never travel through memory; otherwise (the
 and a separate kernel applies the activation.
 
 The spec may ask for another gated activation ("clamped_swish": g sigmoid(alpha g) (u + 1) on a gate clamped
-from above and an up projection clamped on both sides) and other tensor names; the gate/up product then has
+from above and an up projection clamped on both sides) and other tensor names: on the tensor-core path it runs in the same epilogue; elsewhere the gate/up product has
 float32 results and one kernel applies the activation in float32.  :class:`DenseMLP` is the feed-forward
 without a gate, down(act(up x)), with act = max(z, 0)^2.
 """
@@ -46,7 +46,7 @@ class SwiGLU(FeedForward):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors[self.gate_name], tensors[self.up_name]
-        self.fused = (self.act == ops.ACT_SILU and g.dtype == torch.bfloat16 and g.is_cuda
+        self.fused = (g.dtype == torch.bfloat16 and g.is_cuda
                       and self.intermediate_size % ops.SWIGLU_BLOCK == 0 and self.hidden_size % 8 == 0)
         if self.fused:
             self.gate_up = Linear(ops.interleave_gate_up(g, u))
@@ -56,7 +56,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, residual, batch, accumulate: bool = True) -> None:
         if self.fused:
-            a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True)
+            a = ops.gemm_tc(x, self.gate_up.weight, swiglu=True, act=self.act, limit=self.limit, alpha=self.alpha)
         elif self.act == ops.ACT_SILU:
             a = ops.swiglu(self.gate_up(x))
         else:
@@ -90,7 +90,11 @@ class DenseMLP(FeedForward):
         self.down = Linear(tensors[self.down_name])
 
     def forward(self, x, residual, batch, accumulate: bool = True) -> None:
-        a = ops.unary_act(self.up(x, out_dtype=torch.float32), self.act, out_dtype=x.dtype)
+        w = self.up.weight
+        if w.dtype == torch.bfloat16 and ops.gemm_tc_supports(x, w):   # the activation in the product's epilogue
+            a = ops.gemm_tc(x, w, act=self.act)
+        else:
+            a = ops.unary_act(self.up(x, out_dtype=torch.float32), self.act, out_dtype=x.dtype)
         if accumulate:
             self.down.add_to(a, residual)
         else:
