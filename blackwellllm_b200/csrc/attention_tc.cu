@@ -328,10 +328,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
                 bw::tmem_ld_wait();
                 if (row_ok) {
                     if (p.gate) {
+                        // this row's 32 gate values lie side by side: 16-byte loads where the row allows them
                         const size_t token = (size_t)(p.cu_q[r] + tok0 + tok);
+                        const float* grow = p.gate + token * (size_t)p.gate_ld + (size_t)(g * p.G + hg) * p.gate_dv + c0;
+                        if (c0 + 32 <= p.gate_dv && (((uintptr_t)grow) & 15) == 0) {
 #pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            v[c] = __float_as_uint(__uint_as_float(v[c]) * bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, g * p.G + hg, c0 + c));
+                            for (int c = 0; c < 32; c += 4) {
+                                const float4 gv = __ldg(reinterpret_cast<const float4*>(grow + c));
+                                v[c] = __float_as_uint(__fdividef(__uint_as_float(v[c]), 1.f + __expf(-gv.x)));
+                                v[c + 1] = __float_as_uint(__fdividef(__uint_as_float(v[c + 1]), 1.f + __expf(-gv.y)));
+                                v[c + 2] = __float_as_uint(__fdividef(__uint_as_float(v[c + 2]), 1.f + __expf(-gv.z)));
+                                v[c + 3] = __float_as_uint(__fdividef(__uint_as_float(v[c + 3]), 1.f + __expf(-gv.w)));
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                v[c] = __float_as_uint(__uint_as_float(v[c]) * bw::out_gate(p.gate, p.gate_ld, p.gate_dv, token, g * p.G + hg, c0 + c));
+                        }
                     }
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
