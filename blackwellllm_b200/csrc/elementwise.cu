@@ -194,6 +194,18 @@ __global__ void add_planes_kernel(float* __restrict__ x, const float* __restrict
     }
 }
 
+// x = planes[0] + planes[1] + ... (in that order): a product that was WRITTEN as planes, not added
+__global__ void sum_planes_kernel(float* __restrict__ x, const float* __restrict__ planes, int n_planes,
+                                  size_t plane_stride, size_t total) {
+    BW_PDL_TRIGGER();
+    BW_PDL_WAIT();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        add_planes1(v, planes + i, n_planes, plane_stride);
+        x[i] = v;
+    }
+}
+
 // ---------------------------------------------------------------- SwiGLU and other activations
 // in: [T, 2I] with gate in columns [0, I) and up in [I, 2I); out: [T, I] = bw::glu(act, gate, up, limit, alpha)
 // (BW_ACT_SILU: silu(gate) * up).
@@ -554,6 +566,17 @@ BW_EXPORT int bw_add_planes(float* x, const float* planes, int n_planes, long lo
     if (!x || !planes || plane_stride < 0) return BW_ERR_BAD_ARG;
     const long long want = (total + 255) / 256;
     bw::launch(add_planes_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
+               x, planes, n_planes, (size_t)plane_stride, (size_t)total);
+    BW_LAUNCH_CHECK();
+    return 0;
+}
+
+BW_EXPORT int bw_sum_planes(float* x, const float* planes, int n_planes, long long plane_stride, long long total,
+                            void* stream) {
+    if (total <= 0) return 0;
+    if (!x || !planes || plane_stride < 0 || n_planes <= 0) return BW_ERR_BAD_ARG;
+    const long long want = (total + 255) / 256;
+    bw::launch(sum_planes_kernel, dim3((unsigned)(want < 148 * 8 ? want : 148 * 8)), dim3(256), 0, (cudaStream_t)stream,
                x, planes, n_planes, (size_t)plane_stride, (size_t)total);
     BW_LAUNCH_CHECK();
     return 0;

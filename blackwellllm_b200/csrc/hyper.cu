@@ -31,7 +31,8 @@ template <typename OT, int S>
 __global__ void __launch_bounds__(256)
 hc_step_vec4_kernel(float* __restrict__ streams, const float* __restrict__ y, const float* __restrict__ mix,
                     const float* __restrict__ out_w, const float* __restrict__ in_w, const float* __restrict__ gain,
-                    const int* __restrict__ rows, OT* __restrict__ out, int H, float eps, int write_back) {
+                    const int* __restrict__ rows, OT* __restrict__ out, int H, float eps, int write_back,
+               const float* __restrict__ planes, int n_planes, size_t plane_stride, int y_valid) {
     BW_PDL_TRIGGER();
     extern __shared__ __align__(16) float urow[];
     __shared__ float scratch[32];
@@ -49,7 +50,11 @@ hc_step_vec4_kernel(float* __restrict__ streams, const float* __restrict__ y, co
 #pragma unroll
         for (int s = 0; s < S; ++s) old[s] = *reinterpret_cast<const float4*>(xs + (size_t)s * H + c);
         if (yr) {
-            const float4 yv = *reinterpret_cast<const float4*>(yr + c);
+            float4 yv = y_valid ? *reinterpret_cast<const float4*>(yr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 0; p < n_planes; ++p) {   // a product's open sum: its planes are added here, in plane order
+                const float4 pv = *reinterpret_cast<const float4*>(planes + (size_t)p * plane_stride + (size_t)t * H + c);
+                yv.x += pv.x; yv.y += pv.y; yv.z += pv.z; yv.w += pv.w;
+            }
 #pragma unroll
             for (int r = 0; r < S; ++r) {
                 float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -95,7 +100,8 @@ template <typename OT, int S>
 __global__ void __launch_bounds__(256)
 hc_step_kernel(float* __restrict__ streams, const float* __restrict__ y, const float* __restrict__ mix,
                const float* __restrict__ out_w, const float* __restrict__ in_w, const float* __restrict__ gain,
-               const int* __restrict__ rows, OT* __restrict__ out, int H, float eps, int write_back) {
+               const int* __restrict__ rows, OT* __restrict__ out, int H, float eps, int write_back,
+               const float* __restrict__ planes, int n_planes, size_t plane_stride, int y_valid) {
     BW_PDL_TRIGGER();
     extern __shared__ __align__(16) float urow[];   // [H]: the next sublayer's input before its norm
     __shared__ float scratch[32];
@@ -113,7 +119,8 @@ hc_step_kernel(float* __restrict__ streams, const float* __restrict__ y, const f
 #pragma unroll
         for (int s = 0; s < S; ++s) old[s] = xs[(size_t)s * H + c];
         if (yr) {
-            const float yv = yr[c];
+            float yv = y_valid ? yr[c] : 0.f;
+            for (int p = 0; p < n_planes; ++p) yv += planes[(size_t)p * plane_stride + (size_t)t * H + c];
 #pragma unroll
             for (int r = 0; r < S; ++r) {
                 float a = 0.f;
@@ -150,29 +157,34 @@ hc_step_kernel(float* __restrict__ streams, const float* __restrict__ y, const f
 
 template <typename OT, int S>
 int launch_hc(float* streams, const float* y, const float* mix, const float* out_w, const float* in_w, const float* gain,
-              const int* rows, void* out, int n, int H, float eps, int write_back, cudaStream_t s) {
+              const int* rows, void* out, int n, int H, float eps, int write_back, const float* planes, int n_planes,
+              size_t plane_stride, int y_valid, cudaStream_t s) {
     static bool raised[bw::MAX_DEVICES] = {}, raised4[bw::MAX_DEVICES] = {};
     const size_t smem = (size_t)H * sizeof(float);
-    const bool vec = (H & 3) == 0 && (((uintptr_t)streams | (uintptr_t)y | (uintptr_t)gain | (uintptr_t)out) & 15) == 0;
+    const bool vec = (H & 3) == 0 && (plane_stride & 3) == 0 &&
+                     (((uintptr_t)streams | (uintptr_t)y | (uintptr_t)gain | (uintptr_t)out | (uintptr_t)planes) & 15) == 0;
     if (vec) {
         if (smem > 48 * 1024 && bw::allow_dynamic_smem(hc_step_vec4_kernel<OT, S>, 200 * 1024, raised4) != cudaSuccess) return BW_ERR_DRIVER;
         const int threads = H >= 1024 ? 256 : 128;
         bw::launch((hc_step_vec4_kernel<OT, S>), dim3(n), dim3(threads), smem, s, streams, y, mix, out_w, in_w, gain, rows, (OT*)out, H, eps,
-                   write_back);
+                   write_back, planes, n_planes, plane_stride, y_valid);
         BW_LAUNCH_CHECK();
         return 0;
     }
     if (smem > 48 * 1024 && bw::allow_dynamic_smem(hc_step_kernel<OT, S>, 200 * 1024, raised) != cudaSuccess) return BW_ERR_DRIVER;
-    bw::launch((hc_step_kernel<OT, S>), dim3(n), dim3(256), smem, s, streams, y, mix, out_w, in_w, gain, rows, (OT*)out, H, eps, write_back);
+    bw::launch((hc_step_kernel<OT, S>), dim3(n), dim3(256), smem, s, streams, y, mix, out_w, in_w, gain, rows, (OT*)out, H, eps, write_back, planes, n_planes,
+               plane_stride, y_valid);
     BW_LAUNCH_CHECK();
     return 0;
 }
 
 template <typename OT>
 int dispatch_streams(int S, float* streams, const float* y, const float* mix, const float* out_w, const float* in_w,
-                     const float* gain, const int* rows, void* out, int n, int H, float eps, int write_back, cudaStream_t s) {
+                     const float* gain, const int* rows, void* out, int n, int H, float eps, int write_back,
+                     const float* planes, int n_planes, size_t plane_stride, int y_valid, cudaStream_t s) {
     switch (S) {
-#define BW_HC(N) case N: return launch_hc<OT, N>(streams, y, mix, out_w, in_w, gain, rows, out, n, H, eps, write_back, s);
+#define BW_HC(N) case N: return launch_hc<OT, N>(streams, y, mix, out_w, in_w, gain, rows, out, n, H, eps, write_back, planes, n_planes, \
+                                                 plane_stride, y_valid, s);
         BW_HC(1) BW_HC(2) BW_HC(3) BW_HC(4) BW_HC(5) BW_HC(6) BW_HC(7) BW_HC(8)
 #undef BW_HC
     }
@@ -185,16 +197,22 @@ int dispatch_streams(int S, float* streams, const float* y, const float* mix, co
 // mix float32 [S, S] indexed [from, to], out_w float32 [S] (both needed with y); in_w float32 [S] or null;
 // gain float32 [H] or null; rows int32 [n] or null (then n = T rows, all); out [n, H] of out_type (float32
 // when there is no gain).  S up to 8; H * 4 bytes up to 200 KB.
+// planes (with y): n_planes float32 planes [T, H], plane_stride floats apart, that are added to y's rows in plane order as
+// they are read (a matrix product's K splits left unsummed); y_valid == 0: y's own values are not read, the planes are all of it.
 BW_EXPORT int bw_hc_step(float* streams, const float* y, const float* mix, const float* out_w, const float* in_w,
                          const float* gain, const int* rows, void* out, int out_type, int n, int S, int H, float eps,
-                         int write_back, void* stream) {
+                         int write_back, const float* planes, int n_planes, long long plane_stride, int y_valid, void* stream) {
     if (n <= 0) return 0;
+    if (!planes) n_planes = 0;
+    if (n_planes < 0 || plane_stride < 0 || (!y_valid && n_planes == 0 && y)) return BW_ERR_BAD_ARG;
     if (!streams || H <= 0 || (size_t)H * sizeof(float) > 200 * 1024 || (y && (!mix || !out_w)) || (in_w && !out) ||
         (!gain && in_w && out_type != BW_F32) || (rows && write_back))
         return BW_ERR_BAD_ARG;
     if (S < 1 || S > MAX_STREAMS) return BW_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (out_type == BW_F32) return dispatch_streams<float>(S, streams, y, mix, out_w, in_w, gain, rows, out, n, H, eps, write_back, s);
-    if (out_type == BW_BF16) return dispatch_streams<bf16>(S, streams, y, mix, out_w, in_w, gain, rows, out, n, H, eps, write_back, s);
+    if (out_type == BW_F32) return dispatch_streams<float>(S, streams, y, mix, out_w, in_w, gain, rows, out, n, H, eps, write_back, planes,
+                                                           n_planes, (size_t)plane_stride, y_valid, s);
+    if (out_type == BW_BF16) return dispatch_streams<bf16>(S, streams, y, mix, out_w, in_w, gain, rows, out, n, H, eps, write_back, planes,
+                                                           n_planes, (size_t)plane_stride, y_valid, s);
     return BW_ERR_BAD_ARG;
 }

@@ -172,12 +172,15 @@ def logit_transform(logits: torch.Tensor, scale: float = 1.0, softcap: Optional[
 # whichever kernel reads the tensor next: rmsnorm adds them while it normalises; every other
 # function of this module adds them with a kernel of its own first (through _dev); code that reads
 # the tensor by other means calls resolve_pending() before.  At most one sum is outstanding.
+# A product that is WRITTEN to a float32 tensor can be left open the same way (gemm_tc_deferred(...,
+# overwrite=True)): the tensor's own values then do not count, the planes are all of it; hc_step takes
+# such a sum (and an added one) for its y while it reads it.
 
 DEFER_SUMS = os.environ.get("BW_DEFER_SUMS", "1") != "0"
 # Linear.add_to leaves sums open up to this many tokens (measured on a B200: 4 % less step time at 1 to 16
 # tokens, 1.5 % at 24 to 64, 0.5 % at 128, nothing at 256)
 DEFER_MAX_TOKENS = int(os.environ.get("BW_DEFER_MAX_TOKENS", "128"))
-_pending = None          # (target tensor, planes [S, M, N]) or None
+_pending = None          # (target tensor, planes [S, M, N], overwrite) or None
 _plane_buffers = {}
 PLANE_BUFFER_ELEMS = 8 << 20
 _plane_generation = 0    # counts the products that left planes: whoever keeps planes for later checks that they are still the last
@@ -200,9 +203,9 @@ def resolve_pending() -> None:
     global _pending
     if _pending is None:
         return
-    target, planes = _pending
+    target, planes, overwrite = _pending
     _pending = None
-    fn = _fn("elementwise", "bw_add_planes", [c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p])
+    fn = _fn("elementwise", "bw_sum_planes" if overwrite else "bw_add_planes", [c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p])
     _check(fn(_ptr(target), _ptr(planes), planes.shape[0], planes.stride(0), target.numel(), _stream()), "add_planes")
 
 
@@ -246,20 +249,23 @@ def planes_generation() -> int:
     return _plane_generation
 
 
-def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """out += x @ w.T (+ bias), the sum left to the next reader of ``out`` (float32 [M, N], contiguous)."""
+def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                     overwrite: bool = False) -> None:
+    """out += x @ w.T (+ bias), the sum left to the next reader of ``out`` (float32 [M, N], contiguous);
+    ``overwrite``: out = x @ w.T (+ bias) instead (what ``out`` holds does not count)."""
     global _pending
     if out.dtype != torch.float32 or not out.is_contiguous() or out.shape != (x.shape[0], w.shape[0]):
         raise KernelError("gemm_tc_deferred: out must be contiguous float32 [M, N]")
     planes = gemm_tc_planes(x, w, bias)
-    _pending = (out, planes)
+    _pending = (out, planes, bool(overwrite))
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype,
             rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     global _pending
     mine = None              # an outstanding sum into x: added by the kernel below instead of one of its own
-    if _pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape:
+    if (_pending is not None and _pending[0].data_ptr() == x.data_ptr() and _pending[0].shape == x.shape
+            and not _pending[2]):
         mine, _pending = _pending, None
     keep = mine is not None  # the sum stays outstanding unless the kernel below adds it into x
     try:
@@ -1127,9 +1133,15 @@ def hc_step(streams: torch.Tensor, S: int, y: Optional[torch.Tensor] = None, mix
                              u / sqrt(mean(u^2) + eps) * gain (float32 [H]); without ``gain`` the sum itself, float32.
 
     ``rows``: only those rows are computed and ``streams`` is left as it is (the last read of a model)."""
+    global _pending
     _dev(streams, "streams", torch.float32)
     T = streams.shape[0]
     H = streams.shape[1] // S
+    planes, y_valid = None, True
+    if (y is not None and _pending is not None and _pending[0].data_ptr() == y.data_ptr() and _pending[0].shape == y.shape):
+        # y's last product is still in planes: the kernel adds them while it reads y (or takes them for y)
+        (_, planes, overwrite), _pending = _pending, None
+        y_valid = not overwrite
     if streams.shape[1] != S * H:
         raise KernelError("hc_step: streams must be [T, S * H]")
     for name, t, n in (("y", y, T * H), ("mix", mix, S * S), ("out_w", out_w, S), ("in_w", in_w, S), ("gain", gain, H)):
@@ -1146,10 +1158,12 @@ def hc_step(streams: torch.Tensor, S: int, y: Optional[torch.Tensor] = None, mix
     out = None
     if in_w is not None:
         out = torch.empty((n, H), dtype=out_dtype if gain is not None else torch.float32, device=streams.device)
-    fn = _fn("hyper", "bw_hc_step", [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    fn = _fn("hyper", "bw_hc_step", [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_ll, c_int,
+                                                      c_void_p])
     _check(fn(_ptr(streams), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w), _ptr(gain), _ptr(rows), _ptr(out),
               _code(out, "out") if out is not None else F32, n, S, H, float(eps), int(rows is None and y is not None),
-              _stream()), "hc_step")
+              _ptr(planes), planes.shape[0] if planes is not None else 0, planes.stride(0) if planes is not None else 0,
+              int(y_valid), _stream()), "hc_step")
     return out
 
 

@@ -169,6 +169,8 @@ class GQAAttention(Mixer):
                                 self.nh, self.window, self.scale, self.chunk, self.sink, gate)
         if accumulate:
             self.o.add_to(o, residual)
+        elif accumulate is None:
+            self.o.write_to(o, residual)
         else:
             self.o(o, out=residual)
 

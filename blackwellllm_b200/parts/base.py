@@ -17,7 +17,9 @@ Mixer           ``cache_request()`` says what cache it needs (paged keys/values,
                 to ``residual`` (float32 [T,H]) in place; ``owns_cache`` is false
                 when this run reads the cache of another run and must not write it.
                 Mixers and feed-forwards that take ``accumulate=False`` WRITE their output to
-                ``residual`` instead (a block that norms the output before adding it needs that).
+                ``residual`` instead (a block that norms the output before adding it needs that);
+                ``accumulate=None`` writes too, and may leave the last product's sum open
+                (``Linear.write_to``) for a reader that takes open sums (the hyper block's kernel).
 FeedForward     ``forward(x, residual, batch)`` adds its output to ``residual``.
 Block           ``forward(residual, batch, cache)`` arranges norms, mixer and
                 feed-forward.

@@ -166,13 +166,13 @@ class HyperBlock(PreNormBlock):
         x = ops.hc_step(residual, S, y_prev, mix_prev, out_prev, in_w=w_in, gain=self.mixer_norm.gain_f32(),
                         eps=self.mixer_norm.eps, out_dtype=self.ctx.dtype)
         y = torch.empty((T, self.hidden_size), dtype=torch.float32, device=residual.device)
-        self.mixer.forward(x, y, batch, cache, owns_cache, accumulate=False)
+        self.mixer.forward(x, y, batch, cache, owns_cache, accumulate=None)   # written; its sum may stay open for hc_step
         if self.ffn is not None:
             f_in, f_out, f_mix = self.hc[1]
             x = ops.hc_step(residual, S, y, w_mix, w_out, in_w=f_in, gain=self.ffn_norm.gain_f32(), eps=self.ffn_norm.eps,
                             out_dtype=self.ctx.dtype)
             y = torch.empty((T, self.hidden_size), dtype=torch.float32, device=residual.device)
-            self.ffn.forward(x, y, batch, accumulate=False)
+            self.ffn.forward(x, y, batch, accumulate=None)
             w_out, w_mix = f_out, f_mix
         batch.extras["hc_write"] = (y, w_mix, w_out)
 

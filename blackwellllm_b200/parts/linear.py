@@ -33,14 +33,26 @@ class Linear:
             return ops.gemm_tc(x, w, self.bias, out=out, out_dtype=out_dtype, accumulate=accumulate)
         return ops.gemm_simt(x, w, self.bias, out=out, out_dtype=out_dtype, accumulate=accumulate)
 
+    def _may_defer(self, x: torch.Tensor, out: torch.Tensor) -> bool:
+        w = self.weight
+        T = x.shape[0]
+        return (ops.DEFER_SUMS and w.dtype == torch.bfloat16 and x.dtype == w.dtype and T <= ops.DEFER_MAX_TOKENS
+                and T * w.shape[0] <= ops.PLANE_BUFFER_ELEMS and out.dtype == torch.float32
+                and out.is_contiguous() and ops.gemm_tc_supports(x, w))
+
+    def write_to(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """``out = x @ W.T (+ bias)`` (float32) for a reader that takes open sums (``ops.hc_step``): for a few tokens
+        on the tensor-core path the K splits stay planes, as with :meth:`add_to`; whoever reads ``out`` through
+        ``ops`` first gets the sum made."""
+        if self._may_defer(x, out):
+            ops.gemm_tc_deferred(x, self.weight, self.bias, out, overwrite=True)
+        else:
+            self(x, out=out)
+
     def add_to(self, x: torch.Tensor, residual: torch.Tensor) -> None:
         """``residual += x @ W.T (+ bias)`` (float32).  For a few tokens on the tensor-core path the sum
         of the K splits is left to the next reader of ``residual`` (``ops.gemm_tc_deferred``)."""
-        w = self.weight
-        T = x.shape[0]
-        if (ops.DEFER_SUMS and w.dtype == torch.bfloat16 and x.dtype == w.dtype and T <= ops.DEFER_MAX_TOKENS
-                and T * w.shape[0] <= ops.PLANE_BUFFER_ELEMS and residual.dtype == torch.float32
-                and residual.is_contiguous() and ops.gemm_tc_supports(x, w)):
-            ops.gemm_tc_deferred(x, w, self.bias, residual)
+        if self._may_defer(x, residual):
+            ops.gemm_tc_deferred(x, self.weight, self.bias, residual)
         else:
             self(x, out=residual, accumulate=True)

@@ -63,6 +63,8 @@ class SwiGLU(FeedForward):
             a = ops.glu(self.gate_up(x, out_dtype=torch.float32), self.act, self.limit, self.alpha, out_dtype=x.dtype)
         if accumulate:
             self.down.add_to(a, residual)
+        elif accumulate is None:
+            self.down.write_to(a, residual)
         else:
             self.down(a, out=residual)
 
@@ -97,6 +99,8 @@ class DenseMLP(FeedForward):
             a = ops.unary_act(self.up(x, out_dtype=torch.float32), self.act, out_dtype=x.dtype)
         if accumulate:
             self.down.add_to(a, residual)
+        elif accumulate is None:
+            self.down.write_to(a, residual)
         else:
             self.down(a, out=residual)
 

@@ -122,7 +122,7 @@ class RoutedFFN(FeedForward):
     def forward(self, x, residual, batch, accumulate: bool = True) -> None:
         y, pos_of, wt = self._experts(x)
         ops.moe_combine(y, pos_of, wt, residual, not self.scale_input, "add" if accumulate else "write",
-                        x=x if self.n_identity else None)
+                        x=x if self.n_identity else None)     # (accumulate None: written, like False)
         if self.shared is not None:
             self.shared.forward(x, residual, batch)
 
