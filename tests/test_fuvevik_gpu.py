@@ -573,3 +573,71 @@ def test_replay(tmp_path_factory, dtype, family):
         steps = replay.trace_mixed(reqs, max_tokens, seed=3)
     rows = replay.run_trace(folder, dtype, steps, max_tokens, raw["vocab"], page_size=page)
     check_rows(rows, ref, dtype, f"replay {family}", routed(name))
+
+
+# =============================================================================== random configurations
+
+def _random_configuration(rng):
+    """A configuration drawn at random: copies of the stream or none, two to five layers, head counts and sizes (equal
+    and unequal key and value sizes), borrowers of any earlier lender (with the same or another number of query
+    heads), temperature constants or none, every kind of feed-forward or none."""
+    import math
+    layers = []
+    for i in range(rng.randint(2, 5)):
+        lenders = [j for j in range(i) if "kv_from" not in layers[j]["mixer"]]
+        src = rng.choice(lenders) if lenders and rng.random() < 0.45 else None
+        if src is not None:
+            m0 = layers[src]["mixer"]
+            kv, dim, vdim = m0["kv_heads"], m0["dim"], m0["vdim"]
+            heads = kv * rng.choice([1, 2, 4]) if rng.random() < 0.3 else m0["heads"]
+        else:
+            kv = rng.choice([1, 2, 3])
+            heads = kv * rng.choice([1, 2, 4])
+            dim = rng.choice([8, 16, 24, 32, 64, 80])
+            vdim = dim if rng.random() < 0.6 else rng.choice([8, 16, 40, 64])
+        m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": rng.uniform(0.6, 1.6) / math.sqrt(dim)}
+        if rng.random() < 0.8:
+            m["q_temp"] = {"coef": rng.choice([0.1, 0.5, 1.0]), "every": rng.choice([3, 16, 50])}
+        if src is not None:
+            m["kv_from"] = src
+        r = rng.random()
+        if r < 0.15:
+            mlp = None
+        elif r < 0.5:
+            mlp = {"kind": "dense", "ff": rng.choice([24, 64, 100])}
+        else:
+            E, idn = rng.choice([2, 5, 8]), rng.choice([0, 1, 3])
+            mlp = {"kind": "moe", "expert": {"ff": rng.choice([12, 16, 48]), "limit": rng.choice([0.5, 1.5, 7.0])},
+                   "router": {"experts": E, "identity": idn, "top": rng.randint(1, min(4, E + idn))}}
+            if rng.random() < 0.6:
+                mlp["shared"] = {"ff": rng.choice([16, 40]), "limit": rng.choice([0.5, 2.0])}
+        layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    raw = {"architecture": "Fuvevik", "vocab": rng.choice([100, 256]), "width": rng.choice([40, 48, 64, 96]),
+           "norm": {"eps": rng.choice([1e-6, 1e-5])}, "layers": layers}
+    streams = rng.choice([None, 1, 2, 3, 5])
+    if streams is not None:
+        raw["streams"] = streams
+    return raw
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations_float32(seed):
+    """Whole, and in portions with the last tokens one by one, against the plain implementation."""
+    import random
+    from blackwellllm_b200.engine.engine import Engine
+    rng = random.Random(seed)
+    raw = _random_configuration(rng)
+    W = tf.make_tensors(raw, seed=100 + seed, dtype=torch.float32)
+    L = rng.choice([70, 150])
+    ids = tf.prompt(L, raw["vocab"], seed)
+    ref = {"a": plain.plain_forward(raw, W, ids)}
+    ref["b"] = ref["a"]
+    page = rng.choice([8, 16, 32])
+    eng = Engine.from_tensors(raw, W, dtype="float32", page_size=page, num_pages=2 * (L // page + 2), max_requests=2)
+    steps, at = [[("a", ids, 0)]], 0
+    while at < L - 12:
+        n = min(rng.choice([2, 3, 17, 40]), L - 12 - at)
+        steps.append([("b", ids[at:at + n], at)])
+        at += n
+    steps += [[("b", [ids[i]], i)] for i in range(at, L)]
+    check_rows(run_steps(eng, steps), ref, "float32", f"random configuration {seed}: {raw}", False)
