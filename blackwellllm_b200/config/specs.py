@@ -106,7 +106,7 @@ class AttentionSpec:
     names: Tuple[Tuple[str, str], ...] = ()
     # ``qk_norm``: "whole" (above) or "head": every query head and every key head is normed by itself over its
     # ``head_dim`` channels, with one gain vector of that size shared by the heads.  ``q_temperature`` =
-    # (coef, every): the queries of position p are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+    # (coef, every): the queries of position p are multiplied by 1 + coef * log(1 + n), n = whole periods of `every` positions that p + 1 holds.
     # ``sink``: a learned number per query head (tensor "sink") whose exponential joins the softmax's
     # denominator; it has no key and no value and is not scaled.  ``output_gate``: the heads' outputs are
     # multiplied element by element by sigmoid(W_g x) (tensor "g", [heads * value size, hidden]) before the

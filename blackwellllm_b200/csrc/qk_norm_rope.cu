@@ -97,7 +97,7 @@ __device__ __forceinline__ void put4(bf16* p, float4 v) {
 // The same with the norm taken per HEAD: every query head of dq channels is divided by its own root mean
 // square and multiplied by q_gain [dq], one gain vector shared by all heads (k_gain [dq] for the key heads);
 // a null gain: no norm on that side.  After norm and rotation the queries of a token at position p are
-// multiplied by  1 + q_coef * ln(floor((p + 1) / q_every) + 1)  (q_coef == 0: by nothing), a temperature that
+// multiplied by  1 + q_coef * log(1 + n), n = whole periods of q_every positions in p + 1,   (q_coef == 0: by nothing), a temperature that
 // grows with the logarithm of the position.  Rows of qkv are `ld` floats apart and hold the queries first,
 // then (has_kv != 0) keys and values; whatever follows in the row (a gate's projection) is not touched.
 // has_kv == 0: a run that reads another run's keys and values projects none.  One block per token, one warp

@@ -1087,7 +1087,7 @@ def head_norm_rope_append(qkv: torch.Tensor, batch, block_table: torch.Tensor, t
     square and multiplied by ``q_gain`` (float32 [dq], shared by the heads; ``k_gain`` for the key heads).
     ``qkv`` float32 [T, >= nh*dq (+ nkv*dq + nkv*dv with ``has_kv``)]: further columns (a gate's projection) are
     left alone.  ``q_temp`` = (coef, every): after norm and rotation the queries of a token at position p are
-    multiplied by ``1 + coef * ln(floor((p + 1) / every) + 1)``.  Without ``has_kv`` (a run that reads another
+    multiplied by ``1 + coef * log(1 + n)``, n the whole periods of ``every`` positions in p + 1.  Without ``has_kv`` (a run that reads another
     run's keys and values) nothing is appended."""
     _dev(qkv, "qkv", torch.float32); _dev(block_table, "block_table", torch.int32)
     _dev(k_pages, "k_pages"); _dev(v_pages, "v_pages", k_pages.dtype)

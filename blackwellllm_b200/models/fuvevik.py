@@ -10,7 +10,7 @@ sizes; ``mlp``, its feed-forward or null).  What sets the design apart:
 * every norm of the stream stores its gain minus one (``norm.eps`` for all norms);
 * mixer ``attention``: grouped-query softmax attention without rotation; queries and keys normed per head
   (one gain vector shared by the heads); the queries of position p times
-  ``1 + q_temp.coef * ln(floor((p + 1) / q_temp.every) + 1)``; the score scale ``scale``; a learned sink per
+  ``1 + coef * log(1 + n)``, n the number of whole periods of ``q_temp.every`` positions in p + 1 (``coef`` = ``q_temp.coef``); the score scale ``scale``; a learned sink per
   head in the softmax's denominator; the heads' outputs gated by ``sigmoid(W_g x)``; ``kv_from: j`` makes the
   layer read layer j's keys and values (it has no key and value tensors of its own);
 * feed-forward ``dense``: ``down(max(up x, 0)^2)``; ``moe``: a softmax router over ``router.experts`` +

@@ -20,7 +20,7 @@ projection, the route is: projection (float32 out) -> one kernel that norms, rot
 
 Further options, each of which takes that route too: ``qk_norm = "head"`` (every query and key head normed by
 itself, one gain vector of the head's size shared by the heads), ``q_temperature`` (the queries of position p
-times 1 + coef ln(floor((p + 1) / every) + 1)), ``sink`` (one learned number per query head whose exponential
+times 1 + coef log(1 + n), n the whole periods of ``every`` positions in p + 1), ``sink`` (one learned number per query head whose exponential
 joins the softmax's denominator: the kernels add it when they normalise a row), ``output_gate`` (the heads'
 outputs times sigmoid(W_g x) before the output projection; W_g's rows ride in the q/k/v product and the
 attention kernels apply the sigmoid as they write a row), and

@@ -106,7 +106,7 @@ class PositionEncoding(Part):
         all query channels of a token (and all its key channels) are RMS-normed together first; the cache's
         head size may exceed dq and dv (the rest is written as zeros).  ``per_head``: every head is normed by
         itself (gains of dq entries, shared by the heads) and qkv may have further columns, which are left
-        alone; ``q_temp`` (coef, every): the queries are multiplied by 1 + coef ln(floor((p + 1) / every) + 1);
+        alone; ``q_temp`` (coef, every): the queries are multiplied by 1 + coef log(1 + n), n the whole periods of ``every`` positions in p + 1;
         ``has_kv=False``: qkv holds queries only and nothing is appended."""
         raise NotImplementedError
 

@@ -51,7 +51,7 @@ def position_vectors(positions: torch.Tensor, width: int, dtype) -> torch.Tensor
 
 
 def query_temperature(positions: torch.Tensor, q_temp: Optional[dict]) -> torch.Tensor:
-    """1 + coef * ln(floor((p + 1) / every) + 1) per position (ones without the option)."""
+    """1 + coef * log(1 + n) per position p, n the whole periods of ``every`` positions that p + 1 holds (ones without the option)."""
     p = positions.to(torch.float64)
     if not q_temp:
         return torch.ones_like(p)
