@@ -131,6 +131,8 @@ class GQAAttention(Mixer):
             bs = [tensors[n["q_bias"]], tensors[n["k_bias"]], tensors[n["v_bias"]]]
             dt = bs[0].dtype if all(t.dtype == bs[0].dtype for t in bs) else torch.float32
             b = torch.cat([t.to(dt) for t in bs], dim=0)
+            if w.shape[0] > b.numel():    # the gate's rows ride behind q, k, v and have no bias
+                b = torch.cat([b, torch.zeros(w.shape[0] - b.numel(), dtype=dt, device=b.device)])
         wo = tensors[n["o"]]
         if self.qk_norm_eps is not None:
             self.q_gain = tensors[n["q_norm"]].float().contiguous()

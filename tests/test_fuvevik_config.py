@@ -157,3 +157,52 @@ def test_plain_borrowed_keys_are_the_lenders():
     W1 = {k: v for k, v in W.items() if not k.startswith(("l1.", "l2."))}
     plain.plain_forward(raw2, W1, ids, streams_after_layers=streams_b)
     assert torch.allclose(streams_a[0], streams_b[0])
+
+
+# ------------------------------------------------------------------ the new options beside the older ones
+
+def test_attention_options_combine_with_the_older_ones():
+    """The gate and the sink go with biases, a whole-projection norm and a rotation too: the gate's rows ride in the
+    q/k/v product where the per-head kernel follows it (with zero biases for them), else they are a product of their own."""
+    from blackwellllm_b200.config.specs import AttentionSpec, NoPositionSpec, RopeSpec
+    from blackwellllm_b200.parts import BuildContext, build_mixer
+    ctx = BuildContext(torch.device("cpu"), torch.float32)
+    H, nh, nkv, hd = 32, 4, 2, 8
+
+    def tensors(mixer):
+        return {p.name: torch.randn(p.shape) for p in mixer.param_specs()}
+
+    a = build_mixer(AttentionSpec(nh, nkv, hd, qkv_bias=True, position=NoPositionSpec(), qk_norm_eps=1e-5, qk_norm="head",
+                                  sink=True, output_gate=True), H, ctx)
+    names = {p.name: p.shape for p in a.param_specs()}
+    assert names["q_norm.weight"] == (hd,) and names["sinks"] == (nh,) and names["g_proj.weight"] == (nh * hd, H)
+    a.bind(tensors(a))
+    assert a.gate is None and a.qkv.weight.shape == ((nh + 2 * nkv) * hd + nh * hd, H) and a.g_off == (nh + 2 * nkv) * hd
+    assert a.qkv.bias.numel() == a.qkv.weight.shape[0] and float(a.qkv.bias[a.g_off:].abs().max()) == 0.0
+    b = build_mixer(AttentionSpec(nh, nkv, hd, qkv_bias=False, position=RopeSpec(10000.0, hd), qk_norm_eps=1e-5,
+                                  output_gate=True), H, ctx)
+    assert {p.name: p.shape for p in b.param_specs()}["q_norm.weight"] == (nh * hd,)
+    b.bind(tensors(b))
+    assert b.gate is not None and b.qkv.weight.shape == ((nh + 2 * nkv) * hd, H)     # the whole-projection kernel has fixed rows
+    c = build_mixer(AttentionSpec(nh, nkv, hd, qkv_bias=False, position=NoPositionSpec(), qk_norm_eps=1e-5, qk_norm="head",
+                                  shares_kv=True), H, ctx)
+    assert sorted(p.name for p in c.param_specs()) == ["o_proj.weight", "q_norm.weight", "q_proj.weight"]
+    with pytest.raises(ValueError):
+        build_mixer(AttentionSpec(nh, nkv, hd, qkv_bias=True, position=NoPositionSpec(), shares_kv=True), H, ctx)
+    with pytest.raises(ValueError):
+        build_mixer(AttentionSpec(nh, nkv, hd, qkv_bias=False, position=NoPositionSpec(), qk_norm="row"), H, ctx)
+
+
+def test_routed_feed_forward_options_are_checked():
+    from blackwellllm_b200.config.specs import RoutedFFNSpec
+    from blackwellllm_b200.parts import BuildContext, build_ffn
+    ctx = BuildContext(torch.device("cpu"), torch.float32)
+    r = build_ffn(RoutedFFNSpec(4, 5, 16, score="softmax", identity_experts=2, choice_bias="correction"), 32, ctx)
+    shapes = {p.name: p.shape for p in r.param_specs()}
+    assert shapes["router"] == (6, 32) and shapes["correction"] == (6,) and "e3.gate" in shapes and "e4.gate" not in shapes
+    with pytest.raises(ValueError):
+        build_ffn(RoutedFFNSpec(4, 7, 16, identity_experts=2), 32, ctx)               # more choices than outputs
+    with pytest.raises(ValueError):
+        build_ffn(RoutedFFNSpec(4, 2, 16, identity_experts=2, scale_input=True), 32, ctx)
+    with pytest.raises(ValueError):
+        build_ffn(RoutedFFNSpec(4, 2, 16, activation="gelu"), 32, ctx)
